@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define XB_ABI_VERSION 6
+#define XB_ABI_VERSION 7
 
 typedef struct xb_engine xb_engine;
 
@@ -230,8 +230,26 @@ enum {
                           S <- diag(w) S - (a*u)(u^T S) + k v^T, o = S^T r; w = exp(-e^-1/2 sigmoid(W2 tanh(W1 h) + w0))
                           (W1 of m_rank rows), a = sigmoid(.), u = unit k; read-out RMS-normed per head, weighted, gated
                           by sigmoid(g) */
-  XB_MIX_LIGHTNING = 5 /* linear attention with a constant decay per head: S <- decay S + k v^T, o = S^T q, SiLU on
+  XB_MIX_LIGHTNING = 5,/* linear attention with a constant decay per head: S <- decay S + k v^T, o = S^T q, SiLU on
                           q, k, v; read-out RMS-normed over all heads together, weighted, gated by sigmoid(g) */
+  XB_MIX_SOFTMAX = 6   /* causal grouped-query softmax attention over every earlier key, keys and values of different
+                          sizes, rotary positions on the first s_rot_dims entries of each query / key head (pairs
+                          (i, i + dims/2) or (2i, 2i+1), frequencies base^(-2i/dims) rescaled per XB_ROT_SCALE_*, cos and
+                          sin times s_rot_mult).  Each of these is switched by its field: a learned sink per head in the
+                          softmax denominator (s_sink), scores squashed to cap * tanh(score / cap) (s_softcap), the
+                          normalised weights of the heads mixed by an [H, H] matrix before they meet the values (s_talk),
+                          values blended with those of the first blending layer, v <- (1 - l) v + l v_first (s_vmix),
+                          one sigmoid output gate per head (s_gate) */
+};
+
+/* how the rotary frequencies f_i = base^(-2i/dims) of XB_MIX_SOFTMAX are rescaled (l_i = 2 pi / f_i) */
+enum {
+  XB_ROT_SCALE_NONE = 0,
+  XB_ROT_SCALE_BANDS = 1, /* f kept where l < orig / p1, f / factor where l > orig / p0, between them a blend with
+                             s = (orig / l - p0) / (p1 - p0): (1 - s) f / factor + s f   (p0 = low, p1 = high) */
+  XB_ROT_SCALE_RAMP = 2   /* with dim(t) = dims ln(orig / (2 pi t)) / (2 ln base), lo = max(floor(dim(p0)), 0),
+                             hi = min(ceil(dim(p1)), dims - 1), r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1):
+                             f r / factor + f (1 - r)   (p0 = fast, p1 = slow) */
 };
 
 enum {
@@ -241,6 +259,11 @@ enum {
                           experts in `groups` equal groups of neighbours, a group scores the sum of its two best experts and
                           only the `keep_groups` best groups stay eligible; weights = scores * route_scale; plus an
                           always-on shared expert of width shared_ff (0 = none) */
+};
+/* what an expert of XB_FF_MOE computes (ff_act) */
+enum {
+  XB_ACT_GLU_CLAMP = 0,   /* down(g sigmoid(1.702 g) (u + 1)) with the limits above */
+  XB_ACT_SWIGLU = 1       /* down(silu(g) u), no limits */
 };
 
 typedef struct xb_hybrid_layer {
@@ -262,6 +285,18 @@ typedef struct xb_hybrid_layer {
   float route_scale, shared_limit;
   int32_t weights_of;                               /* >= 0: this layer owns no tensors and uses that layer's (with a cache
                                                        and state of its own); -1: its own */
+  int32_t ff_act;                                   /* XB_FF_MOE: XB_ACT_* */
+  int32_t route_input;                              /* XB_FF_MOE: 1 = the routing weight multiplies what the expert reads,
+                                                       sum_e expert_e(w_e h); 0 = its output, sum_e w_e expert_e(h) */
+  /* XB_MIX_SOFTMAX */
+  int32_t s_heads, s_kv_heads, s_dim, s_vdim;
+  int32_t s_rot_dims, s_rot_pairs;                  /* entries that turn (0 = no rotation); XB_ROPE_* pair layout */
+  int32_t s_rot_scaling;                            /* XB_ROT_SCALE_* */
+  int32_t s_sink, s_talk, s_gate;                   /* 0 / 1 each */
+  int32_t s_vmix;                                   /* 0: values as projected; 1: blended with the values of the first layer
+                                                       that sets this (which keeps its own as they are) */
+  float s_scale, s_softcap, s_rot_mult;             /* score = q.k * s_scale; cap 0 = none; cos / sin multiplier */
+  double s_rot_base, s_rot_factor, s_rot_orig, s_rot_p0, s_rot_p1;
 } xb_hybrid_layer;
 
 typedef struct xb_hybrid_desc {
@@ -277,6 +312,13 @@ typedef struct xb_hybrid_desc {
   int32_t block;                     /* XB_BLOCK_*: how a layer's sublayers meet the residual stream */
   int32_t norm_scalar;               /* 1: the stream's norms ("l<i>.norm1", "final.norm") carry one number, used as it is */
   float embed_scale;                 /* the embedding row is multiplied by this (1 = as stored) */
+  int32_t norm_groups;               /* the stream's norms split a row into this many equal consecutive parts, each divided by
+                                        its own root mean square (0 or 1 = the whole row) */
+  int32_t norm_plain;                /* sandwich blocks: 1 = norm weights are used as stored, 0 = stored as offsets from one */
+  float residual_mult;               /* sandwich blocks: x += residual_mult * norm(branch) (0 = 1) */
+  int32_t tied_head;                 /* 1: the logits are products with the embedding table itself (no "head" tensor) */
+  int32_t ff_unfiltered;             /* sandwich blocks: 1 = only the mixer reads through the causal filter ("canon1"); the
+                                        feed-forward reads its norm directly */
 } xb_hybrid_desc;
 
 enum {

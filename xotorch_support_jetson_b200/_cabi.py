@@ -37,7 +37,7 @@ class ModelDesc(C.Structure):
   ]
 
 
-ABI_VERSION = 6
+ABI_VERSION = 7
 
 
 def model_desc(**fields) -> ModelDesc:
@@ -45,7 +45,9 @@ def model_desc(**fields) -> ModelDesc:
   return ModelDesc(struct_size=C.sizeof(ModelDesc), **fields)
 
 
-MIX_DELTA, MIX_PARALLEL, MIX_LATENT, MIX_GDELTA, MIX_LIGHTNING = 1, 2, 3, 4, 5
+MIX_DELTA, MIX_PARALLEL, MIX_LATENT, MIX_GDELTA, MIX_LIGHTNING, MIX_SOFTMAX = 1, 2, 3, 4, 5, 6
+ROT_SCALE_NONE, ROT_SCALE_BANDS, ROT_SCALE_RAMP = 0, 1, 2
+ACT_GLU_CLAMP, ACT_SWIGLU = 0, 1
 FF_RELU2, FF_GLU_CLAMP, FF_MOE = 0, 1, 2
 BLOCK_SANDWICH, BLOCK_PARALLEL = 0, 1
 ST_BF16, ST_F16, ST_F32 = 0, 1, 2   # element types xb_load_named accepts
@@ -66,6 +68,13 @@ class HybridLayer(C.Structure):
     ("n_experts", C.c_int32), ("top", C.c_int32), ("groups", C.c_int32), ("keep_groups", C.c_int32), ("shared_ff", C.c_int32),
     ("route_scale", C.c_float), ("shared_limit", C.c_float),
     ("weights_of", C.c_int32),
+    ("ff_act", C.c_int32), ("route_input", C.c_int32),
+    ("s_heads", C.c_int32), ("s_kv_heads", C.c_int32), ("s_dim", C.c_int32), ("s_vdim", C.c_int32),
+    ("s_rot_dims", C.c_int32), ("s_rot_pairs", C.c_int32), ("s_rot_scaling", C.c_int32),
+    ("s_sink", C.c_int32), ("s_talk", C.c_int32), ("s_gate", C.c_int32), ("s_vmix", C.c_int32),
+    ("s_scale", C.c_float), ("s_softcap", C.c_float), ("s_rot_mult", C.c_float),
+    ("s_rot_base", C.c_double), ("s_rot_factor", C.c_double), ("s_rot_orig", C.c_double), ("s_rot_p0", C.c_double),
+    ("s_rot_p1", C.c_double),
   ]
 
 
@@ -76,6 +85,8 @@ class HybridDesc(C.Structure):
     ("norm_eps", C.c_float), ("logit_softcap", C.c_float), ("compute_fp32", C.c_int32),
     ("max_batch_tokens", C.c_int32), ("max_seqs", C.c_int32), ("max_logit_rows", C.c_int32),
     ("block", C.c_int32), ("norm_scalar", C.c_int32), ("embed_scale", C.c_float),
+    ("norm_groups", C.c_int32), ("norm_plain", C.c_int32), ("residual_mult", C.c_float), ("tied_head", C.c_int32),
+    ("ff_unfiltered", C.c_int32),
   ]
 
 

@@ -1297,6 +1297,10 @@ extern "C" int xb_engine_create_hybrid(const xb_hybrid_desc* desc, const xb_hybr
   XB_CHECK(h.block == XB_BLOCK_SANDWICH || h.block == XB_BLOCK_PARALLEL, "unknown block layout %d", h.block);
   XB_CHECK(h.block == XB_BLOCK_SANDWICH || (h.taps == 0 && h.side_dim == 0), "parallel blocks carry no causal filter or token side input");
   XB_CHECK(h.block == XB_BLOCK_PARALLEL || h.norm_scalar == 0, "sandwich blocks carry a norm weight per channel");
+  XB_CHECK(h.norm_groups >= 0 && h.norm_groups <= HY_MAX_NORM_GROUPS && (h.norm_groups <= 1 || h.dim % h.norm_groups == 0),
+           "norm groups %d must divide dim %d (at most %d)", h.norm_groups, h.dim, HY_MAX_NORM_GROUPS);
+  XB_CHECK(h.block == XB_BLOCK_SANDWICH || (h.norm_groups <= 1 && h.norm_plain == 0 && (h.residual_mult == 0.f || h.residual_mult == 1.f) && h.ff_unfiltered == 0),
+           "grouped norms, plain norm weights, a residual multiplier and an unfiltered feed-forward are options of sandwich blocks");
   xb_engine* e = new xb_engine();
   // the fields of the Llama-shaped description that the shared bookkeeping reads
   e->d = xb_model_desc{};

@@ -16,6 +16,7 @@ struct HyTarget {
   bool f32 = false;          // destination type: fp32 (vectors, filters) or bf16 (matrices, tables)
   long long rows = 0, cols = 0, ld = 0;
   int ndim = 0;
+  bool optional = false;     // a tensor the model can run without (nothing reads it); not counted as missing
 };
 
 struct HyLayer {
@@ -42,6 +43,11 @@ struct HyLayer {
   bf16 *w_uk = nullptr, *w_uv = nullptr, *w_d2 = nullptr, *w_router = nullptr, *t_d2 = nullptr;
   float *b_up = nullptr, *b_down = nullptr, *lat_norm = nullptr, *rot_freq = nullptr, *w0 = nullptr, *hdecay = nullptr;
   int owner = -1;                           // layer whose tensors this one uses (weights_of), -1: its own
+  // rotary-position attention (XB_MIX_SOFTMAX)
+  float *sink = nullptr, *talk = nullptr, *vmix = nullptr;
+  double* rot_freq_d = nullptr;             // [s_rot_dims / 2] rescaled frequencies
+  int vmode = 0;                            // 0: values as projected; 1: leaves its values for later layers; 2: blends with them
+  bool v_all = false;                       // a value row of the pool holds every key head ([page][token][G * dv])
 };
 
 struct HyModel {
@@ -72,6 +78,8 @@ struct HyModel {
   float *qa = nullptr, *gw = nullptr;   // latent attention: queries in the cache's space [T, H * (rank + rot)]; experts: weights [T, E]
   void* ah = nullptr;                  // parallel blocks: the normed stream as a Linear input (both sublayers read it)
   size_t maxQA = 0, maxE = 0, maxM = 0;   // maxM: widest matrix that passes through the m1 / m2 buffers besides the stream's width
+  float* vfirst = nullptr;              // values of the first blending layer for the tokens of this step [T, G * dv]
+  size_t maxGV = 0;
   bool pdl_now = false;
   int recur_lpc = 0;         // XB_HY_LPC=4|8|16 pins the lanes per state column (A/B); 0: by the step's shape
   int use_tc_attn = 1;       // XB_HY_TC_ATTN=0: attention through the per-token kernel everywhere (A/B)
@@ -226,6 +234,80 @@ static int hy_create_mixer(xb_engine* e, int i, bool own, size_t& st, uint64_t& 
   return 0;
 }
 
+// Rotary-position softmax attention: q | k | v | head gates are the rows of one input matrix; sink, head-mixing matrix and
+// blend factor are fp32 vectors; the rescaled rotary frequencies are made here, in double, from the layer's constants.
+static int hy_create_softmax(xb_engine* e, int i, bool own, uint64_t& wbytes, uint64_t& kvpos) {
+  HyModel* hy = e->hy;
+  HyLayer& l = hy->L[i];
+  const xb_hybrid_layer& c = l.d;
+  const xb_hybrid_desc& d = hy->d;
+  const size_t D = d.dim;
+  const std::string p = "l" + std::to_string(i) + ".mix.";
+  const long long H = c.s_heads, G = c.s_kv_heads, dk = c.s_dim, dv = c.s_vdim, rd = c.s_rot_dims;
+  XB_CHECK(own, "layer %d: an attention layer keeps tensors of its own", i);
+  XB_CHECK(d.block == XB_BLOCK_SANDWICH, "layer %d: rotary-position attention belongs to sandwich blocks", i);
+  XB_CHECK(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0, "layer %d: bad attention sizes", i);
+  XB_CHECK(rd >= 0 && rd <= dk && rd % 2 == 0, "layer %d: %lld rotating entries do not fit a head of %lld", i, rd, dk);
+  XB_CHECK(c.s_rot_pairs == XB_ROPE_INTERLEAVED || c.s_rot_pairs == XB_ROPE_HALF_SPLIT, "layer %d: unknown rotary pair layout %d", i, c.s_rot_pairs);
+  XB_CHECK(c.s_softcap >= 0.f && c.s_scale > 0.f, "layer %d: bad score scale %g / soft cap %g", i, c.s_scale, c.s_softcap);
+  l.v_all = c.s_talk != 0 && G > 1;
+  const long long dvo = l.v_all ? G * dv : dv;   // value channels one (token, head) block of the attention kernel carries
+  XB_CHECK(dvo <= 512, "layer %d: %lld value channels per query head (mixed heads read every key head's values; at most 512)", i, dvo);
+  l.off_q = 0; l.off_k = (int)(H * dk); l.off_v = l.off_k + (int)(G * dk); l.off_g = l.off_v + (int)(G * dv);
+  l.n_in = l.off_g + (c.s_gate ? (int)H : 0);
+  l.n_o = (int)(H * dv);
+  XB_TRY(hy_alloc_t(hy, &l.w_in, (size_t)l.n_in * D));
+  XB_TRY(hy_alloc_t(hy, &l.w_o, D * l.n_o));
+  hy_name_rows(hy, p + "q", l.w_in, l.off_q, H * dk, D);
+  hy_name_rows(hy, p + "k", l.w_in, l.off_k, G * dk, D);
+  hy_name_rows(hy, p + "v", l.w_in, l.off_v, G * dv, D);
+  if (c.s_gate) hy_name_rows(hy, p + "g", l.w_in, l.off_g, H, D);
+  hy_name_rows(hy, p + "o", l.w_o, 0, D, l.n_o);
+  if (c.s_sink) { XB_TRY(hy_alloc_t(hy, &l.sink, (size_t)H)); hy_name_vec(hy, p + "sink", l.sink, H); }
+  if (c.s_talk) { XB_TRY(hy_alloc_t(hy, &l.talk, (size_t)(H * H))); hy_name(hy, p + "talk", l.talk, true, H, H, H, 2); }
+  if (c.s_vmix) { XB_TRY(hy_alloc_t(hy, &l.vmix, 1)); hy_name_vec(hy, p + "vmix", l.vmix, 1); }
+  // frequencies f_j = base^(-2j/dims), rescaled (xb200.h: XB_ROT_SCALE_*)
+  const int half = (int)(rd / 2);
+  std::vector<double> fr((size_t)(half > 0 ? half : 1), 0.0);
+  const double base = c.s_rot_base, fac = c.s_rot_factor, orig = c.s_rot_orig, p0 = c.s_rot_p0, p1 = c.s_rot_p1;
+  const double two_pi = 6.283185307179586476925286766559;
+  XB_CHECK(half == 0 || base > 1.0, "layer %d: rotary base %g", i, base);
+  XB_CHECK(c.s_rot_scaling == XB_ROT_SCALE_NONE || (fac > 0.0 && orig > 0.0), "layer %d: bad rotary scaling constants", i);
+  double lo = 0.0, hi = 0.0;
+  if (c.s_rot_scaling == XB_ROT_SCALE_RAMP && half > 0) {
+    XB_CHECK(p0 > 0.0 && p1 > 0.0, "layer %d: bad rotary ramp constants", i);
+    auto at = [&](double t) { return (double)rd * log(orig / (two_pi * t)) / (2.0 * log(base)); };
+    lo = floor(at(p0)); lo = lo < 0.0 ? 0.0 : lo;
+    hi = ceil(at(p1)); hi = hi > (double)(rd - 1) ? (double)(rd - 1) : hi;
+  }
+  for (int j = 0; j < half; ++j) {
+    double f = pow(base, -2.0 * j / (double)rd);
+    if (c.s_rot_scaling == XB_ROT_SCALE_BANDS) {
+      XB_CHECK(p1 != p0 && p0 > 0.0 && p1 > 0.0, "layer %d: bad rotary band constants", i);
+      const double wl = two_pi / f;
+      if (wl < orig / p1) { /* kept */ }
+      else if (wl > orig / p0) f = f / fac;
+      else { const double sm = (orig / wl - p0) / (p1 - p0); f = (1.0 - sm) * f / fac + sm * f; }
+    } else if (c.s_rot_scaling == XB_ROT_SCALE_RAMP) {
+      double r = ((double)j - lo) / (hi - lo > 0.001 ? hi - lo : 0.001);
+      r = r < 0.0 ? 0.0 : (r > 1.0 ? 1.0 : r);
+      f = f / fac * r + f * (1.0 - r);
+    } else {
+      XB_CHECK(c.s_rot_scaling == XB_ROT_SCALE_NONE, "layer %d: unknown rotary scaling %d", i, c.s_rot_scaling);
+    }
+    fr[j] = f;
+  }
+  XB_TRY(hy_alloc_t(hy, &l.rot_freq_d, fr.size()));
+  XB_CUDA(cudaMemcpy(l.rot_freq_d, fr.data(), fr.size() * sizeof(double), cudaMemcpyHostToDevice));
+  const size_t qa = (size_t)(H * dk), ol = (size_t)(H * dvo);
+  if (qa > hy->maxQA) hy->maxQA = qa;
+  if (ol > hy->maxO) hy->maxO = ol;
+  if (c.s_vmix && (size_t)(G * dv) > hy->maxGV) hy->maxGV = (size_t)(G * dv);
+  wbytes += ((size_t)l.n_in * D + D * l.n_o) * 2;
+  kvpos += (uint64_t)G * (dk + dv) * (d.compute_fp32 ? 4 : 2);
+  return 0;
+}
+
 // Gated feed-forwards: dense (gate | up rows of one matrix, biases) or experts (every expert's gate | up rows, then the
 // shared expert's, in one matrix; every expert's down projection side by side as the columns of one matrix).
 static int hy_create_ff(xb_engine* e, int i, bool own, uint64_t& wbytes) {
@@ -234,7 +316,8 @@ static int hy_create_ff(xb_engine* e, int i, bool own, uint64_t& wbytes) {
   const xb_hybrid_layer& c = l.d;
   const size_t D = hy->d.dim, F = c.ff;
   const std::string p = "l" + std::to_string(i) + ".mlp.";
-  XB_CHECK(hy->d.block == XB_BLOCK_PARALLEL, "layer %d: gated feed-forwards belong to parallel blocks", i);
+  XB_CHECK(hy->d.block == XB_BLOCK_PARALLEL || c.ff_kind == XB_FF_MOE, "layer %d: the dense gated feed-forward belongs to parallel blocks", i);
+  XB_CHECK(c.ff_act == XB_ACT_GLU_CLAMP || c.ff_act == XB_ACT_SWIGLU, "layer %d: unknown expert activation %d", i, c.ff_act);
   if (c.ff_kind == XB_FF_GLU_CLAMP) {
     l.n_up = (int)(2 * F); l.n_dn = (int)F;
     if (own) {
@@ -309,7 +392,7 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
                i, c.weights_of);
       l.owner = c.weights_of;
     }
-    XB_CHECK(own || (c.mixer != XB_MIX_DELTA && c.mixer != XB_MIX_PARALLEL), "layer %d: this mixer kind keeps tensors of its own", i);
+    XB_CHECK(own || (c.mixer != XB_MIX_DELTA && c.mixer != XB_MIX_PARALLEL && c.mixer != XB_MIX_SOFTMAX), "layer %d: this mixer kind keeps tensors of its own", i);
     const size_t nd = d.norm_scalar ? 1 : D;   // numbers in a norm of the stream
     if (own) {
       XB_TRY(hy_alloc_t(hy, &l.norm1, nd));
@@ -391,6 +474,8 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
       if ((size_t)l.n_o2 > hy->maxO) hy->maxO = l.n_o2;
       wbytes += ((size_t)l.n_in * D + D * l.n_o + D * l.n_o2) * 2;
       kvpos += (uint64_t)G * (dk + dv) * (d.compute_fp32 ? 4 : 2);
+    } else if (c.mixer == XB_MIX_SOFTMAX) {
+      XB_TRY(hy_create_softmax(e, i, own, wbytes, kvpos));
     } else if (c.mixer == XB_MIX_LATENT || c.mixer == XB_MIX_GDELTA || c.mixer == XB_MIX_LIGHTNING) {
       XB_TRY(hy_create_mixer(e, i, own, st, wbytes, kvpos));
     } else {
@@ -400,6 +485,15 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
     if ((size_t)l.n_o > hy->maxK) hy->maxK = l.n_o;
     if ((size_t)l.n_o2 > hy->maxK) hy->maxK = l.n_o2;
     if (c.ff > 0 && c.ff_kind != XB_FF_RELU2) {
+      if (sandwich) {   // the feed-forward is a sublayer of its own: norm before and after, optionally the causal filter
+        XB_CHECK(own && c.ff_kind == XB_FF_MOE, "layer %d: sandwich blocks take experts with tensors of their own", i);
+        XB_TRY(hy_alloc_t(hy, &l.norm2, D)); hy_name_vec(hy, p + "norm2", l.norm2, D);
+        XB_TRY(hy_alloc_t(hy, &l.norm2b, D)); hy_name_vec(hy, p + "norm2b", l.norm2b, D);
+        if (ct > 0 && !d.ff_unfiltered) {
+          XB_TRY(hy_alloc_t(hy, &l.canon2, D * ct)); hy_name(hy, p + "canon2", l.canon2, true, D, ct, ct, 2);
+          l.st_canon2 = st; st += (size_t)(ct - 1) * D;
+        }
+      }
       XB_TRY(hy_create_ff(e, i, own, wbytes));
     } else if (c.ff > 0) {
       XB_CHECK(own && sandwich, "layer %d: the squared-ReLU feed-forward belongs to sandwich blocks with tensors of their own", i);
@@ -408,7 +502,7 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
       XB_TRY(hy_alloc_t(hy, &l.norm2b, D)); hy_name_vec(hy, p + "norm2b", l.norm2b, D);
       XB_TRY(hy_alloc_t(hy, &l.w_up, F * D)); hy_name_rows(hy, p + "mlp.up", l.w_up, 0, F, D);
       XB_TRY(hy_alloc_t(hy, &l.w_down, D * F)); hy_name_rows(hy, p + "mlp.down", l.w_down, 0, D, F);
-      if (ct > 0) {
+      if (ct > 0 && !d.ff_unfiltered) {
         XB_TRY(hy_alloc_t(hy, &l.canon2, D * ct)); hy_name(hy, p + "canon2", l.canon2, true, D, ct, ct, 2);
         l.st_canon2 = st; st += (size_t)(ct - 1) * D;
       }
@@ -435,7 +529,8 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
     l.lat_norm = o.lat_norm; l.rot_freq = o.rot_freq; l.w0 = o.w0; l.hdecay = o.hdecay; l.canon1 = o.canon1;
   }
   XB_TRY(hy_alloc_t(hy, &hy->embed, (size_t)d.vocab * D)); hy_name_rows(hy, "embed", hy->embed, 0, d.vocab, D);
-  XB_TRY(hy_alloc_t(hy, &hy->head, (size_t)d.vocab * D)); hy_name_rows(hy, "head", hy->head, 0, d.vocab, D);
+  if (d.tied_head) hy->head = hy->embed;   // the logits are products with the embedding table itself
+  else { XB_TRY(hy_alloc_t(hy, &hy->head, (size_t)d.vocab * D)); hy_name_rows(hy, "head", hy->head, 0, d.vocab, D); }
   XB_TRY(hy_alloc_t(hy, &hy->final_norm, d.norm_scalar ? 1 : D)); hy_name_vec(hy, "final.norm", hy->final_norm, d.norm_scalar ? 1 : D);
   if (d.side_dim > 0) {
     const size_t w = (size_t)d.side_dim * d.n_layers;
@@ -462,9 +557,24 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
   XB_TRY(hy_alloc(hy, &hy->a2, Tm * hy->maxK * as));
   XB_TRY(hy_alloc(hy, &hy->head_in, R * D * as));
   if (d.block == XB_BLOCK_PARALLEL) XB_TRY(hy_alloc(hy, &hy->ah, Tm * D * as));
+  {
+    // the first layer that blends values leaves them for the others, whose value rows must have the same width
+    long long first_gv = -1;
+    for (HyLayer& l : hy->L) {
+      if (l.d.mixer != XB_MIX_SOFTMAX || !l.d.s_vmix) continue;
+      const long long gv = (long long)l.d.s_kv_heads * l.d.s_vdim;
+      if (first_gv < 0) { first_gv = gv; l.vmode = 1; }
+      else { XB_CHECK(gv == first_gv, "layers that blend values carry %lld and %lld of them per token", first_gv, gv); l.vmode = 2; }
+    }
+    for (size_t i = 0; i < hy->L.size(); ++i) {   // nothing reads the blend factor of the layer whose values the others take
+      auto it = hy->names.find("l" + std::to_string(i) + ".mix.vmix");
+      if (it != hy->names.end() && hy->L[i].vmode != 2) it->second.optional = true;
+    }
+  }
   if (hy->maxQA > 0) XB_TRY(hy_alloc_t(hy, &hy->qa, Tm * hy->maxQA));
   if (hy->maxLatR > 0 && !d.compute_fp32) XB_TRY(hy_alloc_t(hy, &hy->lat_part, (size_t)HY_LAT_SPLIT_ROWS * (hy->maxLatR + 2)));
   if (hy->maxE > 0) XB_TRY(hy_alloc_t(hy, &hy->gw, Tm * hy->maxE));
+  if (hy->maxGV > 0) XB_TRY(hy_alloc_t(hy, &hy->vfirst, Tm * hy->maxGV));
   hy->cap_head = R * (size_t)d.vocab * 4 > ws_min ? R * (size_t)d.vocab * 4 : ws_min;
   XB_TRY(hy_alloc(hy, (void**)&hy->head_raw, hy->cap_head));
   {
@@ -532,12 +642,17 @@ static int hy_tile(bf16** dst, const bf16* src, size_t rows, size_t K) {
   XB_TRY(alloc_tiled(dst, rows, K));
   return store_tiled(*dst, src, 0, rows, K);
 }
+static int hy_n_missing(const HyModel* hy) {
+  int n = 0;
+  for (const auto& kv : hy->names) n += (!kv.second.optional && !hy->loaded.count(kv.first)) ? 1 : 0;
+  return n;
+}
 static int hy_finalize(xb_engine* e) {
   HyModel* hy = e->hy;
   if (hy->finalized) return 0;
   hy->finalized = true;
   hy->plans.clear();
-  if (hy->d.compute_fp32 || !hy->use_tc || hy->loaded.size() < hy->names.size()) return 0;
+  if (hy->d.compute_fp32 || !hy->use_tc || hy_n_missing(hy) > 0) return 0;
   const size_t D = hy->d.dim;
   auto retile = [&](bf16** dst, const bf16* src, size_t rows, size_t K) -> int {
     if (*dst != nullptr) { cudaFree(*dst); *dst = nullptr; }
@@ -589,7 +704,7 @@ static int hy_missing(xb_engine* e, char* buf, size_t buflen, int* n_missing) {
   std::string out;
   int n = 0;
   for (const auto& kv : e->hy->names) {
-    if (e->hy->loaded.count(kv.first)) continue;
+    if (kv.second.optional || e->hy->loaded.count(kv.first)) continue;
     ++n;
     if (out.size() < 900) out += kv.first + "; ";
   }
@@ -612,6 +727,15 @@ static int hy_reserve(xb_engine* e) {
       const size_t kb = (size_t)e->n_pages * e->page_tokens * (l.d.m_kv_rank + l.d.m_rot_dim) * es;
       XB_TRY(dmalloc(&l.k_pool, kb));
       XB_CUDA(cudaMemset(l.k_pool, 0, kb));
+      continue;
+    }
+    if (l.d.mixer == XB_MIX_SOFTMAX) {   // keys [page][G][token][dk]; values the same way, or [page][token][G * dv] (v_all)
+      const size_t kb = (size_t)e->n_pages * l.d.s_kv_heads * e->page_tokens * l.d.s_dim * es;
+      const size_t vb = (size_t)e->n_pages * l.d.s_kv_heads * e->page_tokens * l.d.s_vdim * es;
+      XB_TRY(dmalloc(&l.k_pool, kb));
+      XB_TRY(dmalloc(&l.v_pool, vb));
+      XB_CUDA(cudaMemset(l.k_pool, 0, kb));
+      XB_CUDA(cudaMemset(l.v_pool, 0, vb));
       continue;
     }
     if (l.d.mixer != XB_MIX_PARALLEL) continue;
@@ -826,14 +950,18 @@ static int hy_attn_tc(xb_engine* e, const HyLayer& l, const BatchMeta& m, const 
 
 template <typename AT>
 static int hy_row_op_launch(xb_engine* e, int T, const RowOpArgs& a, cudaStream_t st);
+// sandwich blocks: x += residual_mult * norm(s1 m1 + s2 m2) * weight, then the next reader's norm into hn (and, as a Linear
+// input, into ha when given).  Weights are offsets from one or plain, norms whole-row or grouped, as the model says.
 template <typename AT>
 static int hy_row_op(xb_engine* e, int T, LinOut m1, float s1, LinOut m2, float s2, const float* bw, float bw_one, const float* nw,
-                     void* xa, cudaStream_t st) {
+                     void* xa, cudaStream_t st, void* ha = nullptr) {
   HyModel* hy = e->hy;
   RowOpArgs a;
-  a.x = hy->x; a.m1 = m1; a.m2 = m2; a.s1 = s1; a.s2 = s2; a.bw = bw; a.bw_one = bw_one; a.nw = nw; a.hn = hy->hn; a.xa = xa;
+  a.x = hy->x; a.m1 = m1; a.m2 = m2; a.s1 = s1; a.s2 = s2; a.bw = bw; a.bw_one = hy->d.norm_plain ? 0.f : bw_one; a.nw = nw; a.hn = hy->hn; a.xa = xa;
   a.eps = hy->d.norm_eps; a.D = hy->d.dim;
-  a.m3 = hy_none(); a.ha = nullptr; a.plain_add = 0; a.nw_mode = 0;
+  a.m3 = hy_none(); a.ha = ha; a.plain_add = 0; a.nw_mode = hy->d.norm_plain ? 1 : 0;
+  a.groups = hy->d.norm_groups > 1 ? hy->d.norm_groups : 1;
+  a.res_mult = hy->d.residual_mult != 0.f ? hy->d.residual_mult : 1.f;
   return hy_row_op_launch<AT>(e, T, a, st);
 }
 template <typename AT>
@@ -896,14 +1024,15 @@ static int hy_latent_mma(xb_engine* e, const HyLayer& l, const BatchMeta& m, int
 // x <- embed * scale;  per layer: h = norm(x) (made by the previous row op), x += mixer(h) + ff(h).
 // The mixers: latent attention (cache = latent + rotated key part, queries folded into the latent space so that a step
 // never rebuilds keys or values of earlier tokens), general delta rule, lightning; feed-forwards: clamped GLU, dense or experts.
+// xin: the normed stream as a Linear input [T, dim] of AT
 template <typename AT>
-static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, cudaStream_t st, LinOut* y) {
+static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, const void* xin, cudaStream_t st, LinOut* y) {
   HyModel* hy = e->hy;
   const xb_hybrid_layer& c = l.d;
   const int D = hy->d.dim;
   AT* a2 = reinterpret_cast<AT*>(hy->a2);
   LinOut U;
-  XB_TRY(hy_linear<AT>(e, hy->ah, D, l.w_up, l.t_up, l.b_up, T, l.n_up, D, hy->P, hy->cap_P, st, &U));
+  XB_TRY(hy_linear<AT>(e, xin, D, l.w_up, l.t_up, l.b_up, T, l.n_up, D, hy->P, hy->cap_P, st, &U));
   // a bf16 matrix out of the tcgen05 Linear (prompts): the activations read and write 16 bytes per thread
   const bool vec = std::is_same<AT, bf16>::value && U.h != nullptr && U.ld % 8 == 0 && l.n_dn % 8 == 0;
   if (c.ff_kind == XB_FF_GLU_CLAMP) {
@@ -917,7 +1046,7 @@ static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, cudaStream_t st
     // router in fp32 whatever the serving type: fp32 accumulation of the products, fp32 logits
     const int chunks = (c.n_experts + 7) / 8;
     XB_TRY(hy_launch(e, hy_router_logits_kernel<AT>, dim3((unsigned)(((long long)T * chunks + 7) / 8)), dim3(256), 0, st,
-                     reinterpret_cast<const AT*>(hy->ah), (long long)D, (const bf16*)l.w_router, hy->m2, T, c.n_experts, D));
+                     reinterpret_cast<const AT*>(xin), (long long)D, (const bf16*)l.w_router, hy->m2, T, c.n_experts, D));
     const LinOut z = hy_plain(hy->m2, c.n_experts);
     const size_t rs = (size_t)4 * (2 * c.n_experts + (c.groups > 0 ? c.groups : 1)) * sizeof(float);
     XB_TRY(hy_launch(e, hy_route_kernel, dim3((T + 3) / 4), dim3(128), rs, st, z, c.n_experts, c.top, c.groups, c.keep_groups, c.route_scale,
@@ -926,10 +1055,10 @@ static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, cudaStream_t st
     const int sf = c.shared_ff > 0 ? c.shared_ff : 0;
     if (vec && c.ff % 8 == 0 && sf % 8 == 0)
       XB_TRY(hy_launch(e, hy_moe_act_vec_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, U.h, U.ld, (const float*)hy->gw, c.n_experts,
-                       c.ff, c.ff_limit, sf, c.shared_limit, reinterpret_cast<bf16*>(hy->a2), (long long)l.n_dn, T));
+                       c.ff, c.ff_limit, sf, c.shared_limit, c.ff_act, c.route_input, reinterpret_cast<bf16*>(hy->a2), (long long)l.n_dn, T));
     else
       XB_TRY(hy_launch(e, hy_moe_act_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, U, (const float*)hy->gw, c.n_experts, c.ff,
-                       c.ff_limit, sf, c.shared_limit, a2, (long long)l.n_dn, T));
+                       c.ff_limit, sf, c.shared_limit, c.ff_act, c.route_input, a2, (long long)l.n_dn, T));
   }
   return hy_linear<AT>(e, a2, l.n_dn, l.w_down, l.t_down, l.b_down, T, D, l.n_dn, hy->m2, hy->cap_m, st, y);
 }
@@ -955,7 +1084,7 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
   auto row_op = [&](LinOut y1, LinOut y2, const float* nw) -> int {
     RowOpArgs a;
     a.x = hy->x; a.m1 = y1; a.m2 = y2; a.m3 = hy_none(); a.s1 = 1.f; a.s2 = 1.f; a.bw = nullptr; a.bw_one = 0.f; a.nw = nw; a.hn = hy->hn;
-    a.xa = nullptr; a.ha = hy->ah; a.eps = d.norm_eps; a.D = D; a.plain_add = 1; a.nw_mode = nwm;
+    a.xa = nullptr; a.ha = hy->ah; a.eps = d.norm_eps; a.D = D; a.plain_add = 1; a.nw_mode = nwm; a.groups = 1; a.res_mult = 1.f;
     return hy_row_op_launch<AT>(e, T, a, st);
   };
   XB_TRY(hy_launch(e, hy_embed_kernel, dim3(T), dim3(128), 0, st, (const int*)e->in_tokens, (const bf16*)hy->embed, hy->x, D, d.vocab,
@@ -989,10 +1118,10 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
       const int far = 1 << 30;
       if (R <= 256)
         XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 8>, dim3(T, H), dim3(32 * aw), asm_bytes, st, Q, 0, -1, (const KT*)l.k_pool,
-                         (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R));
+                         (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R, AttnOpt{nullptr, 0.f, 1}));
       else
         XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 16>, dim3(T, H), dim3(32 * aw), asm_bytes, st, Q, 0, -1, (const KT*)l.k_pool,
-                         (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R));
+                         (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R, AttnOpt{nullptr, 0.f, 1}));
       }
     latent_done:
       XB_TRY(hy_launch(e, hy_head_mm_kernel<AT>, dim3((T + HY_MM_ROWS - 1) / HY_MM_ROWS, H), dim3(128), mm2, st, (const float*)hy->o,
@@ -1023,7 +1152,7 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
                        (const float*)l.head_norm, P, l.off_g, d.norm_eps, a1, (long long)l.n_o, H * dv));
     }
     XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
-    if (c.ff > 0) XB_TRY(hy_ff_parallel<AT>(e, l, T, st, &y2));
+    if (c.ff > 0) XB_TRY(hy_ff_parallel<AT>(e, l, T, hy->ah, st, &y2));
     XB_TRY(row_op(y1, y2, next_norm));
     if (taps != nullptr && taps[li] != nullptr)
       XB_CUDA(cudaMemcpyAsync(taps[li], hy->x, (size_t)T * D * sizeof(float), cudaMemcpyDeviceToDevice, st));
@@ -1038,6 +1167,50 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
       const long long tot = (long long)nr * d.vocab;
       XB_TRY(hy_launch(e, hy_logits_kernel, dim3((unsigned)((tot + 255) / 256)), dim3(256), 0, st, y, d.logit_softcap, e->logits, nr, d.vocab));
     }
+  }
+  return 0;
+}
+
+// Rotary-position softmax attention of one layer: P = [q | k | v | head gates] of the step's rows -> a1 = what the output
+// projection reads.  Rotation, value blending and the cache append are one kernel; the attention runs a block per
+// (token, head) over the pages; mixed heads / head gates follow in a kernel of their own.
+template <typename AT>
+static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, const LinOut& P, const BatchMeta& m, cudaStream_t st) {
+  HyModel* hy = e->hy;
+  const xb_hybrid_layer& c = l.d;
+  typedef typename std::conditional<std::is_same<AT, float>::value, float, bf16>::type KT;
+  AT* a1 = reinterpret_cast<AT*>(hy->a1);
+  const int H = c.s_heads, G = c.s_kv_heads, dk = c.s_dim, dv = c.s_vdim;
+  RotArgs r;
+  r.freq = l.rot_freq_d; r.dims = c.s_rot_dims; r.half = c.s_rot_pairs == XB_ROPE_HALF_SPLIT ? 1 : 0; r.mult = c.s_rot_mult;
+  const int units = (H + G) * (dk - c.s_rot_dims / 2) + G * dv;
+  XB_TRY(hy_launch(e, hy_rope_append_kernel<KT>, dim3(T, (units + 255) / 256), dim3(256), 0, st, P, l.off_q, l.off_k, l.off_v, H, G, dk, dv, r,
+                   hy->qa, (KT*)l.k_pool, (KT*)l.v_pool, l.v_all ? 1 : 0, (const float*)l.vmix, hy->vfirst, l.vmode, m));
+  const int dvo = l.v_all ? G * dv : dv;
+  const AttnOpt opt{c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : G};
+  const bool post = c.s_talk != 0 || c.s_gate != 0;
+  const int aw = 16, far = 1 << 30;   // causal over the whole sequence: the block's warps share out all earlier keys
+  const size_t asm_bytes = (size_t)(((dk + 3) & ~3) + aw * (2 + dvo)) * sizeof(float);
+  const LinOut Q = hy_plain(hy->qa, (long long)H * dk);
+  const KT* kp = (const KT*)l.k_pool;
+  const KT* vp = (const KT*)l.v_pool;
+  const dim3 grid(T, H), block(32 * aw);
+  if (post) {
+    if (dvo <= 256)
+      XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 8>, grid, block, asm_bytes, st, Q, 0, -1, kp, vp, m, H, G, dk, dvo, dk, dvo, far, 0,
+                       c.s_scale, 1.0f, hy->o, (long long)H * dvo, opt));
+    else
+      XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 16>, grid, block, asm_bytes, st, Q, 0, -1, kp, vp, m, H, G, dk, dvo, dk, dvo, far, 0,
+                       c.s_scale, 1.0f, hy->o, (long long)H * dvo, opt));
+    XB_TRY(hy_launch(e, hy_heads_mix_kernel<AT>, dim3(T, (H * dv + 255) / 256), dim3(256), 0, st, (const float*)hy->o,
+                     c.s_talk ? (const float*)l.talk : (const float*)nullptr, P, c.s_gate ? l.off_g : -1, H, l.v_all ? G : 1, dv, a1, (long long)l.n_o));
+  } else {
+    if (dvo <= 256)
+      XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, AT, 8>, grid, block, asm_bytes, st, Q, 0, -1, kp, vp, m, H, G, dk, dvo, dk, dvo, far, 0,
+                       c.s_scale, 1.0f, a1, (long long)l.n_o, opt));
+    else
+      XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, AT, 16>, grid, block, asm_bytes, st, Q, 0, -1, kp, vp, m, H, G, dk, dvo, dk, dvo, far, 0,
+                       c.s_scale, 1.0f, a1, (long long)l.n_o, opt));
   }
   return 0;
 }
@@ -1091,6 +1264,9 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
       XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T, (H + 7) / 8), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o,
                        (const float*)l.head_norm, P, l.off_g, d.norm_eps, 1.0f, a1, (long long)l.n_o, H, dv, 0, 0));
       XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
+    } else if (c.mixer == XB_MIX_SOFTMAX) {
+      XB_TRY(hy_softmax_mixer<AT>(e, l, T, n_seqs, P, m, st));
+      XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
     } else {
       const int H = c.a_heads, G = c.a_kv_heads, dk = c.a_dim, dv = c.a_vdim;
       const int Hr = c.r_heads, rk = c.r_dim, rv = c.r_vdim;
@@ -1123,7 +1299,7 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
         const size_t asm_bytes = (size_t)(((dk + 3) & ~3) + aw * (2 + dv)) * sizeof(float);
         XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, AT, 8>, dim3(T, H), dim3(32 * aw), asm_bytes, st, P, l.off_q, l.off_g,
                          (const KT*)l.k_pool, (const KT*)l.v_pool, m, H, G, dk, dv, dk, dv, c.a_window, c.a_keep_first, c.a_scale, 1.0f, a1,
-                         (long long)l.n_o));
+                         (long long)l.n_o, AttnOpt{nullptr, 0.f, G}));
       }
       const long long ldc = 2LL * Hr * rk + (long long)Hr * rv;
       XB_TRY(hy_launch(e, hy_hgrn_prep_kernel, dim3(T, (2 * Hr * rk + Hr * rv + 255) / 256), dim3(256), 0, st, P, l.off_rq, l.off_rf, l.off_rv, (const float*)l.lower, hy->c,
@@ -1143,11 +1319,17 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
       s2 = c.right_scale;
     }
     // x += norm1b(mixer); then whatever reads x next
+    const bool ff_direct = has_ff && (d.ff_unfiltered || d.taps == 0);   // the feed-forward reads its norm without a filter
     XB_TRY(hy_row_op<AT>(e, T, y1, s1, y2, s2, l.norm1b, 1.f, has_ff ? l.norm2 : (has_side ? nullptr : next_norm),
-                         (!has_ff && has_side && !side_fused) ? (void*)a1 : nullptr, st));
-    if (has_ff) {
+                         (!has_ff && has_side && !side_fused) ? (void*)a1 : nullptr, st, ff_direct ? (void*)a1 : nullptr));
+    if (has_ff && c.ff_kind == XB_FF_MOE) {
+      LinOut dn;
+      if (!ff_direct) XB_TRY(hy_sublayer_input<AT>(e, T, n_seqs, no_span, l.canon2, l.st_canon2, m, st));
+      XB_TRY(hy_ff_parallel<AT>(e, l, T, a1, st, &dn));
+      XB_TRY(hy_row_op<AT>(e, T, dn, 1.f, hy_none(), 0.f, l.norm2b, 1.f, has_side ? nullptr : next_norm, (has_side && !side_fused) ? (void*)a1 : nullptr, st));
+    } else if (has_ff) {
       LinOut u, dn;
-      XB_TRY(hy_sublayer_input<AT>(e, T, n_seqs, no_span, l.canon2, l.st_canon2, m, st));
+      if (!ff_direct) XB_TRY(hy_sublayer_input<AT>(e, T, n_seqs, no_span, l.canon2, l.st_canon2, m, st));
       XB_TRY(hy_linear<AT>(e, a1, D, l.w_up, l.t_up, nullptr, T, c.ff, D, hy->P, hy->cap_P, st, &u));
       const long long n = (long long)T * c.ff;
       if (std::is_same<AT, bf16>::value && u.h != nullptr && u.bias == nullptr && c.ff % 8 == 0 && u.ld % 8 == 0)

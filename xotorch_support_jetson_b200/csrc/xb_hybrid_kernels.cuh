@@ -110,7 +110,24 @@ struct RowOpArgs {
   float eps;
   int D;
   int plain_add, nw_mode;
+  int groups;       // > 1: every norm divides each of `groups` equal consecutive parts of the row by its own root mean square
+  float res_mult;   // the normed branch is multiplied by this before it joins the stream
 };
+#define HY_MAX_NORM_GROUPS 64
+// 1 / sqrt(mean(part^2) + eps) of each part of row[0, D) into ginv: a warp per part, lanes stride the part (a fixed order,
+// so the result does not depend on the launch shape).  Ends with a barrier.
+__device__ __forceinline__ void hy_group_inv(const float* row, int D, int groups, float eps, float* ginv) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5, gs = D / groups;
+  __syncthreads();
+  for (int g = warp; g < groups; g += nw) {
+    const float* p = row + (long long)g * gs;
+    float ss = 0.f;
+    for (int j = lane; j < gs; j += 32) ss = fmaf(p[j], p[j], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) ginv[g] = 1.0f / sqrtf(ss / (float)gs + eps);
+  }
+  __syncthreads();
+}
 __device__ __forceinline__ float hy_norm_weight(const float* nw, int mode, int i) {
   return mode == 0 ? 1.0f + nw[i] : (mode == 1 ? nw[i] : nw[0]);
 }
@@ -126,7 +143,34 @@ __global__ void __launch_bounds__(NT) hy_row_op_kernel(RowOpArgs a) {
   float* x = a.x + t * D;
   const bool branch = a.m1.f != nullptr || a.m1.h != nullptr;
   const bool two = a.m2.f != nullptr || a.m2.h != nullptr;
-  if (branch && a.plain_add) {
+  if (a.groups > 1) {
+    // grouped norms (sandwich form): x += res_mult * gnorm(branch) * bw;  hn = gnorm(x) * nw
+    __shared__ float ginv[HY_MAX_NORM_GROUPS];
+    const int gs = D / a.groups;
+    if (branch) {
+      for (int i = threadIdx.x; i < D; i += NT) {
+        float v = a.s1 * lin_at(a.m1, t, i);
+        if (two) v += a.s2 * lin_at(a.m2, t, i);
+        row[i] = v;
+      }
+      hy_group_inv(row, D, a.groups, a.eps, ginv);
+      for (int i = threadIdx.x; i < D; i += NT) {
+        const float v = x[i] + a.res_mult * (row[i] * ginv[i / gs] * (a.bw[i] + a.bw_one));
+        x[i] = v;
+        row[i] = v;
+      }
+    } else {
+      for (int i = threadIdx.x; i < D; i += NT) row[i] = x[i];
+    }
+    if (a.nw != nullptr) {
+      hy_group_inv(row, D, a.groups, a.eps, ginv);
+      for (int i = threadIdx.x; i < D; i += NT) {
+        const float v = row[i] * ginv[i / gs] * hy_norm_weight(a.nw, a.nw_mode, i);
+        a.hn[t * D + i] = v;
+        if (a.ha != nullptr) act_store<AT>(reinterpret_cast<AT*>(a.ha) + t * D + i, v);
+      }
+    }
+  } else if (branch && a.plain_add) {
     const bool three = a.m3.f != nullptr || a.m3.h != nullptr;
     float s2 = 0.f;
     for (int i = threadIdx.x; i < D; i += NT) {
@@ -160,7 +204,7 @@ __global__ void __launch_bounds__(NT) hy_row_op_kernel(RowOpArgs a) {
     const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
     float s2 = 0.f;
     for (int i = threadIdx.x; i < D; i += NT) {
-      const float v = x[i] + row[i] * inv * (a.bw[i] + a.bw_one);
+      const float v = x[i] + a.res_mult * (row[i] * inv * (a.bw[i] + a.bw_one));
       x[i] = v;
       row[i] = v;
       s2 += v * v;
@@ -169,7 +213,11 @@ __global__ void __launch_bounds__(NT) hy_row_op_kernel(RowOpArgs a) {
     s2 = block_sum<NT>(s2, red);
     if (a.nw != nullptr) {
       const float inv2 = 1.0f / sqrtf(s2 / (float)D + a.eps);
-      for (int i = threadIdx.x; i < D; i += NT) a.hn[t * D + i] = row[i] * inv2 * (1.0f + a.nw[i]);
+      for (int i = threadIdx.x; i < D; i += NT) {
+        const float v = row[i] * inv2 * hy_norm_weight(a.nw, a.nw_mode, i);
+        a.hn[t * D + i] = v;
+        if (a.ha != nullptr) act_store<AT>(reinterpret_cast<AT*>(a.ha) + t * D + i, v);
+      }
     }
   } else {
     float s2 = 0.f;
@@ -852,11 +900,20 @@ __global__ void hy_qg_pack_kernel(LinOut P, int off_q, int nq, int off_g, int ng
 // dv <= 32 * NACC (NACC = 8 or 16 value channels per lane).  Key / value rows of the pools are ldk / ldv elements apart
 // (ldk = dk, ldv = dv for separate pools; a value that is the head of its key row reads the key pool with ldv = ldk).
 // Dynamic shared memory: (dk rounded up to 4) + warps * (2 + dv) floats.
+// AttnOpt: what the rotary-position attention adds.  sink (per head, or nullptr): exp(sink_h) joins the softmax
+// denominator, with no key and no value.  softcap > 0: score <- cap * tanh(score / cap) (after the scale).  v_heads: value
+// heads per page of the value pool; 1 while G > 1 means a value row holds every key head's values side by side
+// ([page][token][G * dv], dv here = that whole width), so that one query head's weights meet all of them.
+struct AttnOpt {
+  const float* sink;
+  float softcap;
+  int v_heads;
+};
 template <typename KT, typename AT, int NACC>
 __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q, int off_gate, const KT* __restrict__ k_pool,
                                                              const KT* __restrict__ v_pool, BatchMeta m, int H, int G, int dk, int dv,
                                                              int ldk, int ldv, int window, int keep_first, float scale, float out_scale,
-                                                             AT* __restrict__ out, long long ld_out) {
+                                                             AT* __restrict__ out, long long ld_out, AttnOpt opt) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float qsm[];
@@ -885,8 +942,12 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
     long long prow = 0;
     if (idx < n_vis) {
       const int kp = idx < n_first ? idx : lo + (idx - n_first);
-      prow = ((long long)pages[kp / m.page_tokens] * G + g) * m.page_tokens + kp % m.page_tokens;
-      sc = (ldk & 7) == 0 ? hy_dot_row<KT>(q, k_pool + prow * ldk, dk) : hy_dot_row_any<KT>(q, k_pool + prow * ldk, dk);
+      const long long pg = pages[kp / m.page_tokens];
+      const int ip = kp % m.page_tokens;
+      const long long krow = (pg * G + g) * m.page_tokens + ip;
+      prow = opt.v_heads == G ? krow : pg * m.page_tokens + ip;   // the value row (shared with the other lanes below)
+      sc = (ldk & 7) == 0 ? hy_dot_row<KT>(q, k_pool + krow * ldk, dk) : hy_dot_row_any<KT>(q, k_pool + krow * ldk, dk);
+      if (opt.softcap > 0.f) sc = opt.softcap * tanhf(sc / opt.softcap);
     }
     const float tmax = warp_max(sc);
     const float nm = fmaxf(mx, tmax);
@@ -954,6 +1015,11 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
   float M = -INFINITY;
   for (int w = 0; w < nw; ++w) M = fmaxf(M, part[(long long)w * (2 + dv)]);
   float L = 0.f;
+  if (opt.sink != nullptr) {
+    const float sk = opt.sink[h];
+    M = fmaxf(M, sk);
+    L = expf(sk - M);
+  }
 #pragma unroll
   for (int c = 0; c < NACC; ++c) acc[c] = 0.f;
   for (int w = 0; w < nw; ++w) {
@@ -976,6 +1042,102 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
       act_store<AT>(out + (long long)row * ld_out + (long long)h * dv + d, v);
     }
   }
+}
+
+// ----------------------------------------------------------------------------- rotary positions, value blending, head mixing
+// Rotation of the first `dims` entries of a head: entry pairs (i, i + dims/2) (half = 1) or (2i, 2i + 1) (half = 0);
+// (u, v) -> (u c - v s, v c + u s) with c, s = mult * cos / sin(pos * freq[i]).  The angle is formed in double and reduced
+// to [-pi, pi] there, so that its error does not grow with the position.
+struct RotArgs {
+  const double* freq;   // [dims / 2]
+  int dims, half;
+  float mult;
+};
+__device__ __forceinline__ void hy_rot_cs(const RotArgs& r, int pos, int i, float* c, float* s) {
+  double a = (double)pos * r.freq[i];
+  a -= 6.283185307179586 * rint(a * 0.15915494309189535);
+  sincosf((float)a, s, c);
+  *c *= r.mult;
+  *s *= r.mult;
+}
+// One token row of an XB_MIX_SOFTMAX layer after its input projection P = [q | k | v | ...]: rotated queries -> qa (fp32
+// [T, H * dk]), rotated keys -> the key pool, values -> the value pool.  vmode 1: the values are also left in vfirst
+// ([T, G * dv] fp32) for later layers of the step; vmode 2: v <- (1 - l) v + l vfirst with l = vmix[0] before they are
+// cached.  v_all: a value row holds all G heads ([page][token][G * dv]) instead of [page][G][token][dv].
+// A thread owns a rotating pair or one entry that does not turn.  grid (T, ceil(units / 256)).
+template <typename KT>
+__global__ void __launch_bounds__(256) hy_rope_append_kernel(LinOut P, int off_q, int off_k, int off_v, int H, int G, int dk, int dv,
+                                                             RotArgs r, float* __restrict__ qa, KT* __restrict__ k_pool,
+                                                             KT* __restrict__ v_pool, int v_all, const float* __restrict__ vmix,
+                                                             float* __restrict__ vfirst, int vmode, BatchMeta m) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const int s = m.tok_seq[row], pos = m.tok_pos[row];
+  const long long page = m.page_table[(long long)m.seq_slot[s] * m.max_pages + pos / m.page_tokens];
+  const int in_page = pos % m.page_tokens;
+  const int hp = r.dims >> 1, per = dk - hp;   // units of one query / key head
+  const int n_qk = (H + G) * per, total = n_qk + G * dv;
+  for (int u = blockIdx.y * blockDim.x + threadIdx.x; u < total; u += blockDim.x * gridDim.y) {
+    if (u < n_qk) {
+      const int hd = u / per, j = u - hd * per;
+      const bool is_q = hd < H;
+      const int h = is_q ? hd : hd - H;
+      const int src = (is_q ? off_q : off_k) + h * dk;
+      float* qo = qa + (long long)row * H * dk + (long long)h * dk;
+      KT* ko = k_pool + ((page * G + h) * m.page_tokens + in_page) * dk;
+      if (j < hp) {
+        const int d0 = r.half ? j : 2 * j, d1 = r.half ? j + hp : 2 * j + 1;
+        const float a = lin_at(P, row, src + d0), b = lin_at(P, row, src + d1);
+        float c, sn;
+        hy_rot_cs(r, pos, j, &c, &sn);
+        const float y0 = a * c - b * sn, y1 = b * c + a * sn;
+        if (is_q) { qo[d0] = y0; qo[d1] = y1; }
+        else { act_store<KT>(ko + d0, y0); act_store<KT>(ko + d1, y1); }
+      } else {
+        const int d = r.dims + (j - hp);
+        const float a = lin_at(P, row, src + d);
+        if (is_q) qo[d] = a;
+        else act_store<KT>(ko + d, a);
+      }
+    } else {
+      const int i = u - n_qk;
+      float v = lin_at(P, row, off_v + i);
+      if (vmode == 1) vfirst[(long long)row * G * dv + i] = v;
+      else if (vmode == 2) { const float lam = vmix[0]; v = (1.0f - lam) * v + lam * vfirst[(long long)row * G * dv + i]; }
+      const int g = i / dv, d = i - g * dv;
+      KT* vo = v_all ? v_pool + (page * m.page_tokens + in_page) * ((long long)G * dv) + i
+                     : v_pool + ((page * G + g) * m.page_tokens + in_page) * dv + d;
+      act_store<KT>(vo, v);
+    }
+  }
+}
+
+// What follows the attention of an XB_MIX_SOFTMAX layer with mixed heads and / or head gates.
+// talk != nullptr: o holds, per token and query head g, that head's softmax weights applied to the values of EVERY key head
+// ([T][H][G * dv]); mixing the weights, w'_h = sum_g talk[h, g] w_g, and applying them to the values of head h's own key
+// head c(h) is the same as  out_h = sum_g talk[h, g] o[g][c(h)]  (both are linear in the weights).  Else o is [T][H][dv].
+// off_gate >= 0: head h is multiplied by sigmoid(P[t, off_gate + h]).  grid (T, ceil(H * dv / 256)).
+template <typename AT>
+__global__ void __launch_bounds__(256) hy_heads_mix_kernel(const float* __restrict__ o, const float* __restrict__ talk, LinOut P, int off_gate,
+                                                           int H, int G, int dv, AT* __restrict__ out, long long ld_out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= H * dv) return;
+  const int h = i / dv, d = i - h * dv;
+  float v;
+  if (talk != nullptr) {
+    const int c = h / (H / G);
+    const float* ot = o + t * ((long long)H * G * dv) + (long long)c * dv + d;
+    v = 0.f;
+    for (int g = 0; g < H; ++g) v = fmaf(talk[h * H + g], ot[(long long)g * G * dv], v);
+  } else {
+    v = o[t * ((long long)H * dv) + i];
+  }
+  if (off_gate >= 0) v *= hy_sigmoid(lin_at(P, t, off_gate + h));
+  act_store<AT>(out + t * ld_out + i, v);
 }
 
 // ----------------------------------------------------------------------------- feed-forward activation, side input, logits
@@ -1317,6 +1479,14 @@ __device__ __forceinline__ float hy_glu_clamp(float g, float u, float limit) {
   u = fminf(fmaxf(u, -limit), limit);
   return g * hy_sigmoid(1.702f * g) * (u + 1.0f);
 }
+// One channel of one expert with routing weight w.  act: XB_ACT_GLU_CLAMP or XB_ACT_SWIGLU (silu(g) u, no limits).
+// on_input: the weight multiplies what the expert reads, and since both projections are linear, (w h) W^T = w (h W^T):
+// gate and up are scaled before the activation; otherwise the weight multiplies the activation (and so the output).
+__device__ __forceinline__ float hy_expert_act(float g, float u, float w, float limit, int act, int on_input) {
+  if (on_input) { g *= w; u *= w; }
+  const float y = act == XB_ACT_SWIGLU ? hy_silu(g) * u : hy_glu_clamp(g, u, limit);
+  return on_input ? y : w * y;
+}
 // U carries [gate (F) | up (F)] (biases on read): out[t, i] = glu(gate_i, up_i).  grid over T * F.
 template <typename AT>
 __global__ void hy_glu_clamp_kernel(LinOut U, int F, float limit, AT* __restrict__ out, long long ld_out, int T) {
@@ -1340,10 +1510,10 @@ __device__ __forceinline__ void hy_load8(const bf16* p, const float* bias, float
     v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w; v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
   }
 }
-__device__ __forceinline__ uint4 hy_glu8(const float* g, const float* u, float limit, float w) {
+__device__ __forceinline__ uint4 hy_glu8(const float* g, const float* u, float limit, float w, int act = XB_ACT_GLU_CLAMP, int on_input = 0) {
   float y[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) y[j] = w * hy_glu_clamp(g[j], u[j], limit);
+  for (int j = 0; j < 8; ++j) y[j] = hy_expert_act(g[j], u[j], w, limit, act, on_input);
   return make_uint4(f2_to_bf2(y[0], y[1]), f2_to_bf2(y[2], y[3]), f2_to_bf2(y[4], y[5]), f2_to_bf2(y[6], y[7]));
 }
 __global__ void hy_glu_clamp_vec_kernel(const bf16* __restrict__ u, long long ld, const float* __restrict__ bias, int F, float limit,
@@ -1361,7 +1531,7 @@ __global__ void hy_glu_clamp_vec_kernel(const bf16* __restrict__ u, long long ld
   *reinterpret_cast<uint4*>(out + t * ld_out + i) = hy_glu8(g, v, limit, 1.0f);
 }
 __global__ void hy_moe_act_vec_kernel(const bf16* __restrict__ u, long long ld, const float* __restrict__ gw, int E, int f, float limit, int sf,
-                                      float limit_s, bf16* __restrict__ out, long long ld_out, int T) {
+                                      float limit_s, int act, int on_input, bf16* __restrict__ out, long long ld_out, int T) {
   pdl_launch_dependents();
   pdl_wait();
   const int W8 = (E * f + sf) >> 3;
@@ -1377,13 +1547,13 @@ __global__ void hy_moe_act_vec_kernel(const bf16* __restrict__ u, long long ld, 
     if (w != 0.f) {
       hy_load8(u + t * ld + 2 * e * f + j, nullptr, g);
       hy_load8(u + t * ld + 2 * e * f + f + j, nullptr, v);
-      r = hy_glu8(g, v, limit, w);
+      r = hy_glu8(g, v, limit, w, act, on_input);
     }
   } else {
     const int j = i - E * f;
     hy_load8(u + t * ld + 2 * E * f + j, nullptr, g);
     hy_load8(u + t * ld + 2 * E * f + sf + j, nullptr, v);
-    r = hy_glu8(g, v, limit_s, 1.0f);
+    r = hy_glu8(g, v, limit_s, 1.0f, act, 0);
   }
   *reinterpret_cast<uint4*>(out + t * ld_out + i) = r;
 }
@@ -1499,11 +1669,11 @@ __global__ void __launch_bounds__(128) hy_route_kernel(LinOut z, int E, int top,
 }
 
 // U carries, expert after expert, [gate_e (f) | up_e (f)], then the shared expert's [gate (sf) | up (sf)].
-// out[t, e * f + i] = gw[t, e] * glu(gate, up; limit) (zero for experts the token does not use),
+// out[t, e * f + i] = hy_expert_act(gate, up, gw[t, e]) (zero for experts the token does not use),
 // out[t, E * f + i] = glu of the shared expert (limit_s): the input of ONE down projection over all experts' columns.
 template <typename AT>
 __global__ void hy_moe_act_kernel(LinOut U, const float* __restrict__ gw, int E, int f, float limit, int sf, float limit_s,
-                                  AT* __restrict__ out, long long ld_out, int T) {
+                                  int act, int on_input, AT* __restrict__ out, long long ld_out, int T) {
   pdl_launch_dependents();
   pdl_wait();
   const int W = E * f + sf;
@@ -1515,10 +1685,10 @@ __global__ void hy_moe_act_kernel(LinOut U, const float* __restrict__ gw, int E,
   if (i < E * f) {
     const int e = i / f, j = i - e * f;
     const float g = gw[t * E + e];
-    if (g != 0.f) v = g * hy_glu_clamp(lin_at(U, t, 2 * e * f + j), lin_at(U, t, 2 * e * f + f + j), limit);
+    if (g != 0.f) v = hy_expert_act(lin_at(U, t, 2 * e * f + j), lin_at(U, t, 2 * e * f + f + j), g, limit, act, on_input);
   } else {
     const int j = i - E * f;
-    v = hy_glu_clamp(lin_at(U, t, 2 * E * f + j), lin_at(U, t, 2 * E * f + sf + j), limit_s);
+    v = hy_expert_act(lin_at(U, t, 2 * E * f + j), lin_at(U, t, 2 * E * f + sf + j), 1.0f, limit_s, act, 0);
   }
   act_store<AT>(out + t * ld_out + i, v);
 }

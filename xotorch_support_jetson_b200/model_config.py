@@ -28,7 +28,7 @@ _DIRECT_FIELDS = (
 _OPTIONAL_FIELDS = (("attention_dropout", "attn_dropout", 0.0), ("attention_bias", "attn_bias", False), ("hidden_act", "hidden_act", "silu"))
 
 
-HYBRID_ARCHITECTURES = ("Refatar", "Bibevik")
+HYBRID_ARCHITECTURES = ("Refatar", "Bibevik", "Pufivik")
 
 
 def is_hybrid(config: dict) -> bool:
@@ -50,6 +50,8 @@ def hybrid_model_config(raw: dict) -> dict:
     raise ValueError(f"unknown architecture {arch!r}")
   if arch == "Bibevik":
     return bibevik_model_config(raw)
+  if arch == "Pufivik":
+    return pufivik_model_config(raw)
   layers = []
   for i, lc in enumerate(raw["layers"]):
     mx, kind = lc["mixer"], lc["type"]
@@ -129,6 +131,66 @@ def bibevik_model_config(raw: dict) -> dict:
     "embed_dim": int(raw["width"]), "vocab_size": int(raw["vocab"]), "num_layers": len(layers),
     "max_seq_len": int(raw.get("max_seq_len", 1 << 20)), "norm_eps": float(raw["norm"]["eps"]),
     "taps": 0, "side_dim": 0, "logit_softcap": 0.0, "layers": layers,
+    "torch_dtype": HF_PRECISION_STR_TO_DTYPE.get(raw.get("torch_dtype", "bfloat16"), torch.bfloat16),
+  }
+
+
+def _rotary(i: int, rot, kind: str) -> dict:
+  """The rotary part of a Pufivik mixer: how many entries of a head turn, the pair layout and the rescaling of the
+  frequencies.  ``attention`` pairs entry i with i + dims/2 and rescales in wavelength bands {factor, low, high, original};
+  ``attention_2`` pairs 2i with 2i + 1 and rescales along a ramp over the pair index {factor, original, fast, slow}, with
+  cos and sin multiplied by 0.1 ln(factor) + 1."""
+  if not rot or not int(rot.get("dims", 0)):
+    return {"rot_dims": 0, "rot_pairs": "half", "rot_scaling": "none", "rot_base": 10000.0, "rot_mult": 1.0,
+            "rot_factor": 1.0, "rot_orig": 1.0, "rot_p0": 0.0, "rot_p1": 0.0}
+  out = {"rot_dims": int(rot["dims"]), "rot_base": float(rot["base"]), "rot_pairs": "half" if kind == "attention" else "interleaved",
+         "rot_scaling": "none", "rot_mult": 1.0, "rot_factor": 1.0, "rot_orig": 1.0, "rot_p0": 0.0, "rot_p1": 0.0}
+  sc = rot.get("scaling")
+  if sc and kind == "attention":
+    out.update(rot_scaling="bands", rot_factor=float(sc["factor"]), rot_orig=float(sc["original"]), rot_p0=float(sc["low"]),
+               rot_p1=float(sc["high"]))
+  elif sc:
+    out.update(rot_scaling="ramp", rot_factor=float(sc["factor"]), rot_orig=float(sc["original"]), rot_p0=float(sc["fast"]),
+               rot_p1=float(sc["slow"]), rot_mult=0.1 * math.log(float(sc["factor"])) + 1.0)
+  return out
+
+
+def pufivik_model_config(raw: dict) -> dict:
+  """A Pufivik ``config.json`` (``width``, ``vocab``, ``embedding.scale``, ``residual_mult``, ``norm`` {eps, groups},
+  ``canon.taps``, ``layers`` [{type, mixer, mlp}]) -> the engine's dict.  Layers are sandwich blocks with plain norm weights,
+  norms in groups, a residual multiplier, a causal filter in front of the mixer only and a tied head.  Both layer types are
+  rotary-position softmax attention {heads, kv_heads, dim, vdim, scale, rot{base, dims, scaling}, v_mix}: ``attention`` adds a
+  sink per head, mixed heads and a sigmoid gate per head; ``attention_2`` a soft cap on the scores.  ``mlp``: null or experts
+  {expert{ff}, router{experts, top}} of the SiLU-gated form whose routing weight (the sigmoid score, not renormalised)
+  multiplies the expert's input."""
+  layers = []
+  for i, lc in enumerate(raw["layers"]):
+    mx, kind = lc["mixer"], lc["type"]
+    if kind not in ("attention", "attention_2"):
+      raise ValueError(f"layer {i}: unknown layer type {kind!r}")
+    first = kind == "attention"
+    lay = {"mixer": "softmax", "heads": int(mx["heads"]), "kv_heads": int(mx["kv_heads"]), "dim": int(mx["dim"]), "vdim": int(mx["vdim"]),
+           "scale": float(mx["scale"]), "softcap": 0.0 if first else float(mx.get("softcap") or 0.0),
+           "sink": first, "talk": first, "gate": first, "v_mix": bool(mx.get("v_mix", False))}
+    lay.update(_rotary(i, mx.get("rot"), kind))
+    mlp = lc.get("mlp")
+    if mlp is None:
+      lay.update({"ff": 0, "ff_kind": "none"})
+    elif mlp.get("kind", "moe") == "moe":
+      lay.update({"ff": int(mlp["expert"]["ff"]), "ff_kind": "moe", "ff_act": "swiglu", "route_input": True, "ff_limit": 0.0,
+                  "experts": int(mlp["router"]["experts"]), "top": int(mlp["router"]["top"]), "groups": 0, "keep_groups": 0,
+                  "route_scale": 1.0, "shared_ff": 0, "shared_limit": 0.0})
+    else:
+      raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+    layers.append(lay)
+  canon, norm = raw.get("canon"), raw["norm"]
+  return {
+    "family": "hybrid", "architecture": "Pufivik", "block": "sandwich", "norm_plain": True, "tied_head": True, "ff_unfiltered": True,
+    "norm_groups": int(norm.get("groups", 1)), "residual_mult": float(raw.get("residual_mult", 1.0)),
+    "embed_scale": float((raw.get("embedding") or {}).get("scale", 1.0)),
+    "embed_dim": int(raw["width"]), "vocab_size": int(raw["vocab"]), "num_layers": len(layers),
+    "max_seq_len": int(raw.get("max_seq_len", 1 << 20)), "norm_eps": float(norm["eps"]),
+    "taps": int(canon["taps"]) if canon else 0, "side_dim": 0, "logit_softcap": 0.0, "layers": layers,
     "torch_dtype": HF_PRECISION_STR_TO_DTYPE.get(raw.get("torch_dtype", "bfloat16"), torch.bfloat16),
   }
 

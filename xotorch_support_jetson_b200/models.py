@@ -128,6 +128,39 @@ _BIBEVIK_1B = _bibevik(2048, 128256, [
    ("latent_attention", _latent(16, 64, 64, 128, 256, base=500000.0), _experts(16, 4, 384, 4, 2, 2048)))
   for i in range(16)])
 
+def _pufivik(width, vocab, layers, groups=2, taps=3, mult=0.7, scale=8.0, eps=1e-6):
+  """A Pufivik config.json: layers is a list of (type, mixer, mlp) entries."""
+  return {"architecture": "Pufivik", "width": width, "vocab": vocab, "embedding": {"scale": scale}, "residual_mult": mult,
+          "norm": {"eps": eps, "groups": groups}, "canon": {"taps": taps},
+          "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in layers]}
+
+
+def _sink_attn(heads, kv, dim, vdim, rot_dims, base=1000000.0, v_mix=True, factor=8.0, low=1.0, high=4.0, original=4096):
+  return {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "v_mix": v_mix,
+          "rot": {"base": base, "dims": rot_dims, "scaling": {"factor": factor, "low": low, "high": high, "original": original}}}
+
+
+def _cap_attn(heads, kv, dim, vdim, rot_dims, base=10000.0, v_mix=True, softcap=50.0, factor=4.0, fast=32.0, slow=1.0, original=1024):
+  return {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "softcap": softcap, "v_mix": v_mix,
+          "rot": {"base": base, "dims": rot_dims, "scaling": {"factor": factor, "fast": fast, "slow": slow, "original": original}}}
+
+
+def _swiglu_experts(n, top, ff):
+  return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": n, "top": top}}
+
+
+_PUFIVIK_TINY = _pufivik(160, 448, [
+  ("attention", _sink_attn(6, 3, 40, 24, 16), _swiglu_experts(6, 2, 48)),
+  ("attention_2", _cap_attn(4, 1, 32, 72, 32), None),
+  ("attention_2", _cap_attn(6, 2, 24, 36, 8, v_mix=False), _swiglu_experts(8, 1, 32)),
+  ("attention", _sink_attn(3, 3, 48, 24, 24), _swiglu_experts(6, 2, 48)),
+], groups=4, taps=4)
+# 1B-class geometry for throughput runs (random weights): the widths of llama-3.2-1b (32 query / 8 key heads of 64), three
+# soft-capped layers to one with sink, mixed heads and head gates; 8 experts of 1024 of which a token uses two
+_PUFIVIK_1B = _pufivik(2048, 128256, [
+  (("attention", _sink_attn(32, 8, 64, 64, 32), _swiglu_experts(8, 2, 1024)) if i % 4 == 1 else
+   ("attention_2", _cap_attn(32, 8, 64, 64, 64), _swiglu_experts(8, 2, 1024))) for i in range(16)], scale=45.0)
+
 # model id -> {layers, repo:{EngineClassName: hf repo}, hf_config}
 model_cards = {
   "llama-3.2-1b": {"layers": 16, "repo": {ENGINE_CLASS_NAME: "unsloth/Llama-3.2-1B-Instruct"},
@@ -151,6 +184,8 @@ model_cards = {
   "refatar-1b": {"layers": 16, "repo": {ENGINE_CLASS_NAME: "synthetic/refatar-1b"}, "hf_config": _REFATAR_1B},
   "bibevik-tiny": {"layers": 5, "repo": {ENGINE_CLASS_NAME: "synthetic/bibevik-tiny"}, "hf_config": _BIBEVIK_TINY},
   "bibevik-1b": {"layers": 16, "repo": {ENGINE_CLASS_NAME: "synthetic/bibevik-1b"}, "hf_config": _BIBEVIK_1B},
+  "pufivik-tiny": {"layers": 4, "repo": {ENGINE_CLASS_NAME: "synthetic/pufivik-tiny"}, "hf_config": _PUFIVIK_TINY},
+  "pufivik-1b": {"layers": 16, "repo": {ENGINE_CLASS_NAME: "synthetic/pufivik-1b"}, "hf_config": _PUFIVIK_1B},
   "mistral-tiny": {"layers": 4, "repo": {ENGINE_CLASS_NAME: "synthetic/mistral-tiny"},
                    "hf_config": _mistral(320, 5, 1, 640, 4, head_dim=64, vocab=1280)},
 }

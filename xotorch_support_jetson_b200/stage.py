@@ -134,7 +134,20 @@ class StageRuntime:
       if lc.get("ff_kind") == "moe":
         L.n_experts, L.top, L.groups, L.keep_groups = lc["experts"], lc["top"], lc["groups"], lc["keep_groups"]
         L.route_scale, L.shared_ff, L.shared_limit = lc["route_scale"], lc["shared_ff"], lc["shared_limit"]
-      if lc["mixer"] in ("latent", "gdelta", "lightning"):
+        L.ff_act = {"glu_clamp": _cabi.ACT_GLU_CLAMP, "swiglu": _cabi.ACT_SWIGLU}[lc.get("ff_act", "glu_clamp")]
+        L.route_input = int(bool(lc.get("route_input", False)))
+      if lc["mixer"] == "softmax":
+        L.mixer = _cabi.MIX_SOFTMAX
+        L.s_heads, L.s_kv_heads, L.s_dim, L.s_vdim = lc["heads"], lc["kv_heads"], lc["dim"], lc["vdim"]
+        L.s_scale, L.s_softcap = lc["scale"], lc.get("softcap", 0.0)
+        L.s_sink, L.s_talk, L.s_gate, L.s_vmix = (int(bool(lc.get(k))) for k in ("sink", "talk", "gate", "v_mix"))
+        L.s_rot_dims = lc.get("rot_dims", 0)
+        L.s_rot_pairs = _cabi.ROPE_HALF_SPLIT if lc.get("rot_pairs", "half") == "half" else _cabi.ROPE_INTERLEAVED
+        L.s_rot_scaling = {"none": _cabi.ROT_SCALE_NONE, "bands": _cabi.ROT_SCALE_BANDS, "ramp": _cabi.ROT_SCALE_RAMP}[lc.get("rot_scaling", "none")]
+        L.s_rot_mult = lc.get("rot_mult", 1.0)
+        L.s_rot_base, L.s_rot_factor, L.s_rot_orig = lc.get("rot_base", 10000.0), lc.get("rot_factor", 1.0), lc.get("rot_orig", 1.0)
+        L.s_rot_p0, L.s_rot_p1 = lc.get("rot_p0", 0.0), lc.get("rot_p1", 0.0)
+      elif lc["mixer"] in ("latent", "gdelta", "lightning"):
         L.mixer = {"latent": _cabi.MIX_LATENT, "gdelta": _cabi.MIX_GDELTA, "lightning": _cabi.MIX_LIGHTNING}[lc["mixer"]]
         L.m_heads, L.m_dim = lc["heads"], lc["dim"]
         if lc["mixer"] == "latent":
@@ -161,7 +174,10 @@ class StageRuntime:
       norm_eps=config["norm_eps"], logit_softcap=config["logit_softcap"], compute_fp32=int(dtype == "float32"),
       max_batch_tokens=max_batch_tokens, max_seqs=max_seqs, max_logit_rows=self.max_logit_rows,
       block=_cabi.BLOCK_PARALLEL if config.get("block") == "parallel" else _cabi.BLOCK_SANDWICH,
-      norm_scalar=int(bool(config.get("norm_scalar", False))), embed_scale=float(config.get("embed_scale", 1.0)))
+      norm_scalar=int(bool(config.get("norm_scalar", False))), embed_scale=float(config.get("embed_scale", 1.0)),
+      norm_groups=int(config.get("norm_groups", 1)), norm_plain=int(bool(config.get("norm_plain", False))),
+      residual_mult=float(config.get("residual_mult", 1.0)), tied_head=int(bool(config.get("tied_head", False))),
+      ff_unfiltered=int(bool(config.get("ff_unfiltered", False))))
     self.first_from_mlp = self.last_to_attn = False
     self.is_first = self.is_last = True
     self.desc, self._layers = d, lays

@@ -208,6 +208,59 @@ def random_bibevik_state(cfg: dict, seed: int = 0, dtype: torch.dtype = torch.bf
   return out
 
 
+def pufivik_param_shapes(cfg: dict) -> Dict[str, tuple]:
+  """name -> shape of every tensor of a Pufivik config.json (the head is the embedding table: no tensor of its own)."""
+  D, V = cfg["width"], cfg["vocab"]
+  taps = (cfg.get("canon") or {}).get("taps", 0)
+  sh = {"embed": (V, D), "final.norm": (D,)}
+  for i, lc in enumerate(cfg["layers"]):
+    p, m = f"l{i}.", lc["mixer"]
+    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    sh.update({p + "norm1": (D,), p + "norm1b": (D,), p + "mix.q": (H * dk, D), p + "mix.k": (G * dk, D), p + "mix.v": (G * dv, D),
+               p + "mix.o": (D, H * dv)})
+    if taps:
+      sh[p + "canon1"] = (D, taps)
+    if m.get("v_mix"):
+      sh[p + "mix.vmix"] = ()
+    if lc["type"] == "attention":
+      sh.update({p + "mix.talk": (H, H), p + "mix.sink": (H,), p + "mix.g": (H, D)})
+    mlp = lc.get("mlp")
+    if mlp:
+      F, E = mlp["expert"]["ff"], mlp["router"]["experts"]
+      sh.update({p + "norm2": (D,), p + "norm2b": (D,), p + "mlp.router": (E, D)})
+      for e in range(E):
+        sh.update({f"{p}mlp.e{e}.gate": (F, D), f"{p}mlp.e{e}.up": (F, D), f"{p}mlp.e{e}.down": (D, F)})
+  return sh
+
+
+def random_pufivik_state(cfg: dict, seed: int = 0, dtype: torch.dtype = torch.bfloat16, gain: float = 1.0,
+                         device: str = "cpu") -> Dict[str, torch.Tensor]:
+  """Seeded random Pufivik weights: matrices N(0, gain^2 / in), norm weights 1 + N(0, 0.1^2), filters N(0, 0.3^2), sinks
+  N(0, 1), head-mixing matrices identity + N(0, 0.3^2), blend factors in (0.2, 0.8), routers spread so that the scores
+  differ, embedding rows N(0, 1 / width) (the design scales them up again)."""
+  out = {}
+  for idx, (name, shape) in enumerate(sorted(pufivik_param_shapes(cfg).items())):
+    g = torch.Generator(device=device).manual_seed(seed * 1000003 + idx)
+    rn = lambda: torch.randn(shape, generator=g, device=device)  # noqa: E731
+    leaf = name.split(".")[-1]
+    if leaf.startswith("norm"):
+      t = 1.0 + 0.1 * rn()
+    elif leaf == "canon1":
+      t = 0.3 * rn()
+    elif leaf == "sink":
+      t = rn()
+    elif leaf == "talk":
+      t = torch.eye(shape[0], device=device) + 0.3 * rn()
+    elif leaf == "vmix":
+      t = 0.2 + 0.6 * torch.rand(shape, generator=g, device=device)
+    elif leaf == "router":
+      t = 2.0 * gain * rn() / (shape[-1] ** 0.5)
+    else:
+      t = gain * rn() / (shape[-1] ** 0.5)
+    out[name] = t.to(dtype)
+  return out
+
+
 def write_random_checkpoint(path: Path, cfg: dict, seed: int = 0, std: float = 0.02,
                             norm_jitter: float = 0.0, shard_bytes: int = 4 << 30,
                             peaked_head: float = 0.0) -> Path:
@@ -220,6 +273,8 @@ def write_random_checkpoint(path: Path, cfg: dict, seed: int = 0, std: float = 0
     state = random_refatar_state(cfg, seed=seed)
   elif cfg.get("architecture") == "Bibevik":
     state = random_bibevik_state(cfg, seed=seed)
+  elif cfg.get("architecture") == "Pufivik":
+    state = random_pufivik_state(cfg, seed=seed)
   else:
     state = random_hf_state(cfg, seed=seed, std=std, norm_jitter=norm_jitter, peaked_head=peaked_head)
   files, cur, cur_bytes = [], {}, 0

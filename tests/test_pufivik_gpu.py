@@ -1,0 +1,474 @@
+"""The Pufivik design on the native hybrid engine against the plain restatement in tests/pufivik_oracle.py: small
+configurations and random weights made here, every mechanism alone and at other sizes, cached decoding, portions, batches,
+slot and page reuse, a far key, a sink and a score cap made visible, the first tokens, long decoding, greedy generation
+through the serving engine and the trace runner."""
+import asyncio
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import pufivik_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = {"float32": 2e-4, "bfloat16": 6e-2}
+
+
+def bands(factor=8.0, low=1.0, high=4.0, original=64):
+  return {"factor": factor, "low": low, "high": high, "original": original}
+
+
+def ramp(factor=4.0, fast=8.0, slow=1.0, original=48):
+  return {"factor": factor, "fast": fast, "slow": slow, "original": original}
+
+
+def sink_attn(heads=4, kv=2, dim=24, vdim=20, dims=16, base=100.0, scaling="default", v_mix=True, scale=None):
+  rot = {"base": base, "dims": dims}
+  if scaling is not None:
+    rot["scaling"] = bands() if scaling == "default" else scaling
+  return "attention", {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale or dim ** -0.5, "v_mix": v_mix, "rot": rot}
+
+
+def cap_attn(heads=4, kv=2, dim=16, vdim=20, dims=8, base=50.0, scaling="default", v_mix=True, scale=None, softcap=5.0):
+  rot = {"base": base, "dims": dims}
+  if scaling is not None:
+    rot["scaling"] = ramp() if scaling == "default" else scaling
+  return "attention_2", {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale or dim ** -0.5, "softcap": softcap,
+                         "v_mix": v_mix, "rot": rot}
+
+
+def experts(n=6, top=2, ff=40):
+  return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": n, "top": top}}
+
+
+def config(layers, width=96, vocab=200, groups=3, taps=4, mult=0.6, scale=5.0, eps=1e-5):
+  cfg = {"architecture": "Pufivik", "width": width, "vocab": vocab, "embedding": {"scale": scale}, "residual_mult": mult,
+         "norm": {"eps": eps, "groups": groups}, "layers": [{"type": m[0], "mixer": m[1], "mlp": f} for m, f in layers]}
+  if taps:
+    cfg["canon"] = {"taps": taps}
+  return cfg
+
+
+MIXED = config([(cap_attn(), experts()), (sink_attn(), None), (cap_attn(heads=6, kv=3, dim=8, vdim=40, dims=8, v_mix=False), experts(n=5, top=3, ff=24)),
+                (sink_attn(heads=2, kv=1, dim=32, vdim=40, dims=32, v_mix=False), experts(n=4, top=1)),
+                (cap_attn(heads=6, kv=2, dim=12, vdim=20, dims=4), None)])
+
+
+def weights(cfg, seed=0):
+  from xotorch_support_jetson_b200.synth import random_pufivik_state
+  return random_pufivik_state(cfg, seed=seed)
+
+
+def stage(cfg, w, dtype="float32", page=8, seqs=4, cap=640, per_seq=1280):
+  from xotorch_support_jetson_b200.model_config import hybrid_model_config
+  from xotorch_support_jetson_b200.shard import Shard
+  from xotorch_support_jetson_b200.stage import StageRuntime
+  c = hybrid_model_config(cfg)
+  nl = c["num_layers"]
+  st = StageRuntime(Shard("pufivik-test", 0, nl - 1, nl), c, max_batch_tokens=cap, max_seqs=seqs, max_tokens_per_seq=per_seq,
+                    page_tokens=page, dtype=dtype, max_logit_rows=cap)
+  st.load_state(w)
+  return st
+
+
+def toks(n, vocab, seed=0):
+  g = torch.Generator().manual_seed(seed)
+  return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def run(st, slot, ids, pos, rows=None):
+  t = torch.tensor(ids, dtype=torch.int32, device="cuda")
+  rows = list(range(len(ids))) if rows is None else rows
+  out = st.forward([slot], [len(ids)], [pos], tokens=t, want_rows=rows)
+  return None if out is None else out.cpu().double()
+
+
+def rel(got, ref):
+  return float((got - ref).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt())
+
+
+def rows_off(got, ref, tol):
+  size = ref.pow(2).mean().sqrt()
+  return int(((got - ref).pow(2).mean(dim=-1).sqrt() / size > tol).sum())
+
+
+def has_experts(cfg):
+  return any(l["mlp"] for l in cfg["layers"])
+
+
+def logits(cfg, w, ids):
+  return O.forward(cfg, w, ids)
+
+
+@pytest.fixture(scope="module")
+def lib(built_lib):
+  return built_lib
+
+
+# ----------------------------------------------------------------------------- each mechanism alone, other sizes
+ALONE = {
+  "sink_attention": config([(sink_attn(), None)]),
+  "sink_attention_odd_sizes": config([(sink_attn(heads=6, kv=2, dim=10, vdim=7, dims=6, base=30.0), None)], width=50, vocab=77, groups=5, taps=2),
+  "sink_attention_one_key_head": config([(sink_attn(heads=3, kv=1, dim=16, vdim=24, dims=16), None)], groups=1, taps=1),
+  "sink_attention_every_head_its_own_keys": config([(sink_attn(heads=3, kv=3, dim=12, vdim=12, dims=4, scaling=None), None)], mult=1.0),
+  "sink_attention_no_rotation_wide_values": config([(sink_attn(heads=4, kv=4, dim=8, vdim=120, dims=0, scaling=None), None)], taps=0),
+  "sink_attention_bands_all_three": config([(sink_attn(dim=32, dims=32, base=10000.0, scaling=bands(4.0, 1.0, 8.0, 256)), None)]),
+  "cap_attention": config([(cap_attn(), None)]),
+  "cap_attention_odd_sizes": config([(cap_attn(heads=5, kv=1, dim=10, vdim=6, dims=10, base=7.0), None)], width=50, vocab=77, groups=2, taps=5),
+  "cap_attention_tight_cap_large_scale": config([(cap_attn(scale=2.0, softcap=1.5), None)], scale=9.0),
+  "cap_attention_no_cap_no_scaling": config([(cap_attn(softcap=0.0, scaling=None), None)], groups=1),
+  "cap_attention_ramp_inside": config([(cap_attn(dim=32, dims=32, base=10000.0, scaling=ramp(16.0, 32.0, 1.0, 512)), None)]),
+  "cap_attention_wide_head": config([(cap_attn(heads=2, kv=1, dim=160, vdim=136, dims=64), None)], width=64, groups=4),
+  "experts": config([(cap_attn(), experts())]),
+  "experts_top1_of_many": config([(cap_attn(), experts(n=20, top=1, ff=8))], taps=3),
+  "experts_all_used": config([(sink_attn(), experts(n=3, top=3, ff=56))]),
+  "blended_values": config([(cap_attn(v_mix=False), None), (sink_attn(heads=2, kv=2, dim=16, vdim=30), None), (cap_attn(heads=6, kv=2, vdim=30), None),
+                            (cap_attn(v_mix=False, vdim=12), None), (sink_attn(heads=6, kv=2, dim=8, vdim=30, dims=8), None)]),
+  "mixed": MIXED,
+}
+
+
+@pytest.mark.parametrize("name", sorted(ALONE))
+def test_mechanism_against_oracle(lib, name):
+  cfg = ALONE[name]
+  w = weights(cfg, seed=3)
+  ids = toks(70, cfg["vocab"], seed=1)
+  ref, layers = O.forward(cfg, w, ids, return_layers=True)
+  for dtype in ("float32", "bfloat16"):
+    st = stage(cfg, w, dtype)
+    taps = [torch.zeros(len(ids), cfg["width"], device="cuda") for _ in cfg["layers"]]
+    t = torch.tensor(ids, dtype=torch.int32, device="cuda")
+    got = st.forward([1], [len(ids)], [0], tokens=t, want_rows=list(range(len(ids))), taps=taps).cpu().double()
+    st.close()
+    if dtype == "bfloat16" and has_experts(cfg):
+      # a token whose routing is a near tie may pick another expert once activations are rounded: a few such rows among
+      # the 70; the float32 pass has none
+      assert rows_off(got, ref, TOL[dtype]) <= 3, (name, dtype)
+      continue
+    for i, l in enumerate(layers):
+      assert rel(taps[i].cpu().double(), l) < TOL[dtype], (name, dtype, "layer", i)
+    assert rel(got, ref) < TOL[dtype], (name, dtype)
+
+
+# ----------------------------------------------------------------------------- cache and state
+@pytest.fixture(scope="module")
+def mixed(lib):
+  w = weights(MIXED, seed=5)
+  st = stage(MIXED, w, "float32")
+  yield MIXED, w, st
+  st.close()
+
+
+def test_prefill_equals_token_by_token(mixed):
+  cfg, w, st = mixed
+  ids = toks(60, cfg["vocab"], seed=2)
+  ref = logits(cfg, w, ids)
+  whole = run(st, 0, ids, 0)
+  st.release_slot(0)
+  single = torch.cat([run(st, 0, [t], p) for p, t in enumerate(ids)])
+  st.release_slot(0)
+  assert rel(whole, ref) < TOL["float32"] and rel(single, ref) < TOL["float32"]
+  assert rel(single, whole) < 5e-5
+
+
+@pytest.mark.parametrize("cuts", [[2, 37, 2, 5, 1, 1, 30, 2], [1, 1, 1, 2, 3, 70], [40, 40], [3] * 26 + [2], [17, 16, 2, 15, 31]])
+def test_portions(mixed, cuts):
+  cfg, w, st = mixed
+  ids = toks(sum(cuts), cfg["vocab"], seed=4)
+  ref = logits(cfg, w, ids)
+  out, p = [], 0
+  for c in cuts:
+    out.append(run(st, 2, ids[p:p + c], p))
+    p += c
+  st.release_slot(2)
+  assert rel(torch.cat(out), ref) < TOL["float32"]
+
+
+def test_batch_of_unequal_requests_equals_each_alone(mixed):
+  cfg, w, st = mixed
+  a, b, c = toks(33, cfg["vocab"], 7), toks(9, cfg["vocab"], 8), toks(50, cfg["vocab"], 9)
+  ra, rb, rc = (logits(cfg, w, x) for x in (a, b, c))
+  t1 = torch.tensor(a[:20] + b, dtype=torch.int32, device="cuda")
+  o1 = st.forward([0, 3], [20, 9], [0, 0], tokens=t1, want_rows=list(range(29))).cpu().double()
+  t2 = torch.tensor(a[20:] + c[:1], dtype=torch.int32, device="cuda")
+  o2 = st.forward([0, 1], [13, 1], [20, 0], tokens=t2, want_rows=list(range(14))).cpu().double()
+  t3 = torch.tensor(c[1:], dtype=torch.int32, device="cuda")
+  o3 = st.forward([1], [49], [1], tokens=t3, want_rows=list(range(49))).cpu().double()
+  for s in (0, 1, 3):
+    st.release_slot(s)
+  assert rel(torch.cat([o1[:20], o2[:13]]), ra) < TOL["float32"]
+  assert rel(o1[20:], rb) < TOL["float32"]
+  assert rel(torch.cat([o2[13:], o3]), rc) < TOL["float32"]
+  # decode rows of several requests in one step (the serving call: last row of every sequence), slots in any order
+  st.forward([2, 0], [len(a) - 1, len(b) - 1], [0, 0], tokens=torch.tensor(a[:-1] + b[:-1], dtype=torch.int32, device="cuda"), want_rows=[])
+  last = st.forward([0, 2], [1, 1], [len(b) - 1, len(a) - 1], tokens=torch.tensor([b[-1], a[-1]], dtype=torch.int32, device="cuda")).cpu().double()
+  st.release_slot(0), st.release_slot(2)
+  assert rel(last[0:1], rb[-1:]) < TOL["float32"] and rel(last[1:2], ra[-1:]) < TOL["float32"]
+
+
+def test_slot_and_pages_reused_after_release(mixed):
+  cfg, w, st = mixed
+  free0 = st.counters()["kv_pages_free"]
+  a, b = toks(90, cfg["vocab"], 11), toks(41, cfg["vocab"], 12)
+  run(st, 1, a[:50], 0), run(st, 1, a[50:], 50)
+  assert st.counters()["kv_pages_free"] < free0
+  st.release_slot(1)
+  assert st.counters()["kv_pages_free"] == free0
+  got = torch.cat([run(st, 1, b[:17], 0), run(st, 1, b[17:], 17)])   # same slot, recycled pages, an old filter tail behind it
+  st.release_slot(1)
+  assert rel(got, logits(cfg, w, b)) < TOL["float32"]
+
+
+def test_first_tokens_and_single_token_prompt(mixed):
+  cfg, w, st = mixed
+  for n in (1, 2, 3, 4, 5):
+    ids = toks(n, cfg["vocab"], 20 + n)
+    assert rel(run(st, 0, ids, 0), logits(cfg, w, ids)) < TOL["float32"]
+    st.release_slot(0)
+    got = torch.cat([run(st, 0, [t], i) for i, t in enumerate(ids)])
+    st.release_slot(0)
+    assert rel(got, logits(cfg, w, ids)) < TOL["float32"]
+
+
+def test_long_decoding(mixed):
+  """350 decoded tokens behind a 300-token prompt: every step reads all earlier positions across many 8-token pages and
+  more than one 512-key round of the attention block; rotations reach positions near 650."""
+  cfg, w, st = mixed
+  ids = toks(650, cfg["vocab"], 31)
+  ref = logits(cfg, w, ids)
+  run(st, 3, ids[:300], 0, rows=[])
+  got = torch.cat([run(st, 3, [t], 300 + i) for i, t in enumerate(ids[300:])])
+  st.release_slot(3)
+  assert rel(got, ref[300:]) < TOL["float32"]
+  assert float((got - ref[300:]).abs().max()) < 2e-3 * float(ref.abs().max())
+
+
+# ----------------------------------------------------------------------------- edges made visible
+def planted(kind):
+  """One attention layer in which the token with id 1 leaves a key that every later query scores far above all others
+  (through an entry of the head that does not rotate) and a large value: a query that misses it -- a page border, a tile
+  border of the kernel, a lost cache row, the first position -- changes the logits by far more than rounding does."""
+  mk = sink_attn if kind == "attention" else cap_attn
+  extra = {} if kind == "attention" else {"softcap": 40.0}
+  cfg = config([(mk(heads=2, kv=1, dim=12, vdim=8, dims=8, scale=1.0, **extra), None)], width=32, vocab=50, scale=1.0, groups=1, taps=2)
+  w = {k: v.float() for k, v in weights(cfg, seed=9).items()}
+  w["embed"] *= 32 ** 0.5
+  w["embed"][:, 0] = 0.0
+  w["embed"][:, 1] = 2.0                       # a channel that every token carries: queries are built on it
+  w["embed"][1] *= 0.0
+  w["embed"][1, 0] = 6.0                       # the planted token: one large channel that no other token has
+  w["embed"][1, 1] = 2.0
+  w["l0.norm1"][:] = 1.0
+  w["l0.canon1"][:] = 0.0                      # the filter passes the norm through
+  w["l0.mix.k"][:, 0] = 0.0
+  w["l0.mix.k"][11, :] = 0.0
+  w["l0.mix.k"][11, 0] = 3.0                   # the key's last entry (not rotated) reads the planted channel
+  w["l0.mix.q"][11::12, :] = 0.0
+  w["l0.mix.q"][11::12, 1] = 4.0               # every head's last query entry is large and positive for every token
+  w["l0.mix.v"][:, 0] = 2.0
+  if kind == "attention":
+    w["l0.mix.sink"][:] = 0.0
+  return cfg, {k: v.to(torch.bfloat16) for k, v in w.items()}
+
+
+@pytest.mark.parametrize("kind", ["attention", "attention_2"])
+def test_far_key_at_page_and_tile_borders_and_first_positions(lib, kind):
+  cfg, w = planted(kind)
+  st = stage(cfg, w, "float32", page=8)
+  n = 70
+  for at in (0, 1, 7, 8, 9, 15, 16, 31, 32, 33, 40):
+    ids = [(5 + 3 * i) % 48 + 2 for i in range(n)]
+    ids[at] = 1
+    ref = logits(cfg, w, ids)
+    ids2 = list(ids)
+    ids2[at] = 2
+    assert rel(logits(cfg, w, ids2)[at + 1:], ref[at + 1:]) > 0.05          # the planted key matters to every later token
+    whole = run(st, 0, ids, 0)
+    st.release_slot(0)
+    assert rel(whole, ref) < TOL["float32"], (at, "prompt")
+    cut = at + 1
+    run(st, 0, ids[:cut], 0, rows=[])
+    dec = torch.cat([run(st, 0, [t], cut + i) for i, t in enumerate(ids[cut:])])
+    st.release_slot(0)
+    assert rel(dec, ref[cut:]) < TOL["float32"], (at, "decoded")
+  st.close()
+
+
+@pytest.mark.parametrize("kind", ["attention", "attention_2"])
+def test_far_key_among_hundreds(lib, kind):
+  """The planted key lies 500 to 600 positions back, at the borders of the block's 512-key rounds."""
+  cfg, w = planted(kind)
+  st = stage(cfg, w, "float32", page=8)
+  for at in (3, 88, 89):
+    ids = [(7 + 5 * i) % 48 + 2 for i in range(610)]
+    ids[at] = 1
+    ref = logits(cfg, w, ids)
+    run(st, 1, ids[:590], 0, rows=[])
+    got = torch.cat([run(st, 1, ids[590:597], 590), run(st, 1, ids[597:599], 597)] + [run(st, 1, [t], 599 + i) for i, t in enumerate(ids[599:])])
+    st.release_slot(1)
+    assert rel(got, ref[590:]) < TOL["float32"], at
+    ids2 = list(ids)
+    ids2[at] = 2
+    assert rel(logits(cfg, w, ids2)[590:], ref[590:]) > 0.05
+  st.close()
+
+
+def test_sink_takes_its_share_and_is_not_mixed(lib):
+  """Large sinks take most of the softmax mass of some heads: the outputs shrink accordingly (an engine that left the sink
+  out, scaled it, or counted it per key would be off by far more than rounding), in prompts and in decoding."""
+  cfg = config([(sink_attn(heads=4, kv=2, dim=16, vdim=16, dims=8), None)], width=64, groups=2)
+  w = {k: v.float() for k, v in weights(cfg, seed=12).items()}
+  w["l0.mix.sink"] = torch.tensor([4.0, -3.0, 1.5, 6.0])
+  w = {k: v.to(torch.bfloat16) for k, v in w.items()}
+  ids = toks(80, cfg["vocab"], seed=13)
+  ref = logits(cfg, w, ids)
+  w0 = dict(w)
+  w0["l0.mix.sink"] = torch.full((4,), -30.0).to(torch.bfloat16)
+  assert rel(logits(cfg, w0, ids), ref) > 0.05
+  st = stage(cfg, w, "float32")
+  whole = run(st, 0, ids, 0)
+  st.release_slot(0)
+  run(st, 0, ids[:40], 0, rows=[])
+  dec = torch.cat([run(st, 0, [t], 40 + i) for i, t in enumerate(ids[40:])])
+  st.close()
+  assert rel(whole, ref) < TOL["float32"] and rel(dec, ref[40:]) < TOL["float32"]
+
+
+def test_rotation_pairs_scaling_and_positions(lib):
+  """Scores that come from the rotating entries alone, low bases (large angles), both pair layouts with their rescaled
+  frequencies, positions up to 300 in a prompt, portions and single tokens; the oracle with every position shifted by one
+  does not agree, so the positions matter."""
+  cfg = config([(sink_attn(heads=2, kv=1, dim=8, vdim=8, dims=8, base=7.0, scale=1.0, scaling=bands(3.0, 1.0, 4.0, 40)), None),
+                (cap_attn(heads=2, kv=1, dim=8, vdim=8, dims=8, base=5.0, scale=1.0, softcap=20.0, scaling=ramp(3.0, 4.0, 1.0, 30)), None)],
+               width=32, vocab=50, groups=2)
+  w = weights(cfg, seed=4)
+  ids = toks(300, cfg["vocab"], seed=6)
+  ref = logits(cfg, w, ids)
+  shifted = O.forward(cfg, w, ids, pos0=1)
+  assert rel(shifted[50:], ref[50:]) > 0.02
+  st = stage(cfg, w, "float32", page=16)
+  got = torch.cat([run(st, 0, ids[:130], 0), run(st, 0, ids[130:132], 130)] + [run(st, 0, [t], 132 + i) for i, t in enumerate(ids[132:])])
+  st.close()
+  assert rel(got, ref) < TOL["float32"]
+
+
+def test_filter_tail_across_portions_of_two_tokens(lib):
+  """A five-tap filter with large weights: the four inputs before a portion come from the slot, also when the portion is
+  shorter than the filter and when the slot was used by another request before."""
+  cfg = config([(cap_attn(), None), (sink_attn(), experts())], taps=5)
+  w = {k: v.float() for k, v in weights(cfg, seed=15).items()}
+  for i in range(2):
+    w[f"l{i}.canon1"] *= 4.0
+  w = {k: v.to(torch.bfloat16) for k, v in w.items()}
+  st = stage(cfg, w, "float32")
+  run(st, 0, toks(23, cfg["vocab"], 1), 0, rows=[])
+  st.release_slot(0)
+  ids = toks(41, cfg["vocab"], 16)
+  ref = logits(cfg, w, ids)
+  out, p = [], 0
+  for c in [2, 2, 1, 3, 2, 1, 1, 1, 6, 2, 20]:
+    out.append(run(st, 0, ids[p:p + c], p))
+    p += c
+  st.close()
+  assert rel(torch.cat(out), ref) < TOL["float32"]
+
+
+# ----------------------------------------------------------------------------- bf16 serving
+def test_bf16_prompt_equals_token_by_token(lib):
+  """bf16 serving at sizes the tensor-core Linears take: a 300-token prompt (bf16 matrices out of the Linears) against the
+  same tokens one at a time (split-K planes) and against the oracle."""
+  cfg = config([(cap_attn(heads=4, kv=2, dim=64, vdim=64, dims=32), None), (sink_attn(heads=4, kv=2, dim=64, vdim=64, dims=64), None),
+                (cap_attn(heads=8, kv=2, dim=32, vdim=64, dims=32), None)], width=128, groups=2)
+  w = weights(cfg, seed=13)
+  ids = toks(300, cfg["vocab"], seed=14)
+  ref = logits(cfg, w, ids)
+  st = stage(cfg, w, "bfloat16", page=64)
+  whole = run(st, 0, ids, 0)
+  st.release_slot(0)
+  run(st, 0, ids[:150], 0, rows=[])
+  single = torch.cat([run(st, 0, [t], 150 + i) for i, t in enumerate(ids[150:])])
+  st.close()
+  assert rel(whole, ref) < TOL["bfloat16"] and rel(single, ref[150:]) < TOL["bfloat16"]
+  assert rel(single, whole[150:]) < TOL["bfloat16"]
+
+
+# ----------------------------------------------------------------------------- the serving engine
+def test_greedy_generation_through_the_engine(lib, tmp_path):
+  """B200ShardInferenceEngine (infer_prompt / sample / infer_tensor, its request table and slot scheduler) on the registered
+  pufivik-tiny model, checkpoint written and loaded from disk, against greedy decoding of the oracle."""
+  from safetensors.torch import load_file
+  from xotorch_support_jetson_b200.b200_engine import B200ShardInferenceEngine
+  from xotorch_support_jetson_b200.models import build_full_shard, model_cards
+  from xotorch_support_jetson_b200.synth import LocalShardDownloader
+  mid = "pufivik-tiny"
+  eng = B200ShardInferenceEngine(LocalShardDownloader(root=tmp_path, seed=2), device=0, max_seqs=4, max_tokens_per_seq=256,
+                                 max_batch_tokens=16, page_tokens=16, dtype="float32")
+  shard = build_full_shard(mid, "B200ShardInferenceEngine")
+  cfg = model_cards[mid]["hf_config"]
+  prompt = [3 + (11 * i) % 440 for i in range(37)]          # 37 tokens through 16-row native calls: chunked prefill
+
+  async def go():
+    out, state = await eng.infer_prompt("g1", shard, "<ids:" + ",".join(map(str, prompt)) + ">")
+    ids, lg = [], [out]
+    for _ in range(12):
+      tok = await eng.sample(out, temp=0.0)
+      ids.append(int(tok.item()))
+      out, state = await eng.infer_tensor("g1", shard, tok.reshape(1, 1), state)
+      lg.append(out)
+    eng.end_request("g1")
+    return ids, lg
+
+  ids, lg = asyncio.run(go())
+  w = {}
+  for f in sorted((tmp_path / "synthetic--pufivik-tiny").glob("*.safetensors")):
+    w.update(load_file(str(f)))
+  seq = list(prompt)
+  for step, tok in enumerate(ids):
+    ref = logits(cfg, w, seq)[-1]
+    assert rel(torch.from_numpy(lg[step][0]).double(), ref) < TOL["float32"]
+    top2 = ref.topk(2).values
+    if float(top2[0] - top2[1]) > 1e-3:
+      assert tok == int(ref.argmax()), step
+    seq.append(tok)
+
+
+# ----------------------------------------------------------------------------- the command line
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_runner_replays_steps(lib, tmp_path, dtype):
+  """bin/trace_run on a model folder written here: a whole prompt, a prompt in portions with single tokens behind it, a
+  request that ends and whose slot the next one takes."""
+  import subprocess
+  import sys
+  from pathlib import Path
+  from safetensors.torch import save_file
+  cfg = config([(cap_attn(), experts(n=4, top=2)), (sink_attn(), None), (cap_attn(heads=2, kv=2, v_mix=True, vdim=20), experts(n=3, top=1))],
+               width=64, vocab=120, groups=2, taps=3)
+  w = weights(cfg, seed=17)
+  model = tmp_path / "model"
+  model.mkdir()
+  (model / "config.json").write_text(json.dumps(cfg))
+  save_file({k: v.contiguous() for k, v in w.items()}, str(model / "model.safetensors"))
+  a, b = toks(50, cfg["vocab"], 41), toks(31, cfg["vocab"], 42)
+  steps = [
+    {"step": 0, "entries": [{"id": "a", "tokens": a, "want": [49, 0, 20]}], "end": ["a"]},
+    {"step": 1, "entries": [{"id": "b", "tokens": b[:17], "want": []}], "end": []},
+    {"step": 2, "entries": [{"id": "b", "tokens": b[17:19], "want": [0, 1]}], "end": []},
+  ] + [{"step": 3 + i, "entries": [{"id": "b", "tokens": [t], "want": [0]}], "end": (["b"] if 19 + i == len(b) - 1 else [])}
+       for i, t in enumerate(b[19:])]
+  root = Path(__file__).resolve().parent.parent
+  ra, rb = logits(cfg, w, a), logits(cfg, w, b)
+  out = tmp_path / "out"
+  p = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(model), "--dtype", dtype, "--out", str(out),
+                      "--max-tokens", "64"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+  assert p.returncode == 0, p.stderr[-2000:]
+  assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+  rd = lambda i: torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, cfg["vocab"])).double()  # noqa: E731
+  tol = TOL[dtype]
+  assert not (out / "1.f32").exists()
+  got = torch.cat([rd(0), rd(2)] + [rd(3 + i) for i in range(len(b) - 19)])
+  ref = torch.cat([ra[[49, 0, 20]], rb[17:]])
+  if dtype == "bfloat16":
+    assert rows_off(got, ref, tol) <= 1       # a routing near-tie may fall the other way once activations are rounded
+  else:
+    assert rel(got, ref) < tol

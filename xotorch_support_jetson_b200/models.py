@@ -151,8 +151,8 @@ def _swiglu_experts(n, top, ff):
 
 _PUFIVIK_TINY = _pufivik(160, 448, [
   ("attention", _sink_attn(6, 3, 40, 24, 16), _swiglu_experts(6, 2, 48)),
-  ("attention_2", _cap_attn(4, 1, 32, 72, 32), None),
-  ("attention_2", _cap_attn(6, 2, 24, 36, 8, v_mix=False), _swiglu_experts(8, 1, 32)),
+  ("attention_2", _cap_attn(6, 3, 32, 24, 32), None),
+  ("attention_2", _cap_attn(4, 1, 24, 36, 8, v_mix=False), _swiglu_experts(8, 1, 32)),
   ("attention", _sink_attn(3, 3, 48, 24, 24), _swiglu_experts(6, 2, 48)),
 ], groups=4, taps=4)
 # 1B-class geometry for throughput runs (random weights): the widths of llama-3.2-1b (32 query / 8 key heads of 64), three

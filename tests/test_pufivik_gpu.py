@@ -245,15 +245,15 @@ def test_long_decoding(mixed):
 
 
 # ----------------------------------------------------------------------------- edges made visible
-def planted(kind):
+def planted(kind, heads=2, kv=1, dim=12, vdim=8, dims=8, width=32):
   """One attention layer in which the token with id 1 leaves a key that every later query scores far above all others
   (through an entry of the head that does not rotate) and a large value: a query that misses it -- a page border, a tile
   border of the kernel, a lost cache row, the first position -- changes the logits by far more than rounding does."""
   mk = sink_attn if kind == "attention" else cap_attn
   extra = {} if kind == "attention" else {"softcap": 40.0}
-  cfg = config([(mk(heads=2, kv=1, dim=12, vdim=8, dims=8, scale=1.0, **extra), None)], width=32, vocab=50, scale=1.0, groups=1, taps=2)
+  cfg = config([(mk(heads=heads, kv=kv, dim=dim, vdim=vdim, dims=dims, scale=1.0, **extra), None)], width=width, vocab=50, scale=1.0, groups=1, taps=2)
   w = {k: v.float() for k, v in weights(cfg, seed=9).items()}
-  w["embed"] *= 32 ** 0.5
+  w["embed"] *= width ** 0.5
   w["embed"][:, 0] = 0.0
   w["embed"][:, 1] = 2.0                       # a channel that every token carries: queries are built on it
   w["embed"][1] *= 0.0
@@ -262,10 +262,10 @@ def planted(kind):
   w["l0.norm1"][:] = 1.0
   w["l0.canon1"][:] = 0.0                      # the filter passes the norm through
   w["l0.mix.k"][:, 0] = 0.0
-  w["l0.mix.k"][11, :] = 0.0
-  w["l0.mix.k"][11, 0] = 3.0                   # the key's last entry (not rotated) reads the planted channel
-  w["l0.mix.q"][11::12, :] = 0.0
-  w["l0.mix.q"][11::12, 1] = 4.0               # every head's last query entry is large and positive for every token
+  w["l0.mix.k"][dim - 1::dim, :] = 0.0
+  w["l0.mix.k"][dim - 1::dim, 0] = 3.0         # every key head's last entry (not rotated) reads the planted channel
+  w["l0.mix.q"][dim - 1::dim, :] = 0.0
+  w["l0.mix.q"][dim - 1::dim, 1] = 4.0         # every head's last query entry is large and positive for every token
   w["l0.mix.v"][:, 0] = 2.0
   if kind == "attention":
     w["l0.mix.sink"][:] = 0.0
@@ -337,16 +337,19 @@ def test_sink_takes_its_share_and_is_not_mixed(lib):
 
 def test_rotation_pairs_scaling_and_positions(lib):
   """Scores that come from the rotating entries alone, low bases (large angles), both pair layouts with their rescaled
-  frequencies, positions up to 300 in a prompt, portions and single tokens; the oracle with every position shifted by one
-  does not agree, so the positions matter."""
+  frequencies, positions up to 300 in a prompt, portions and single tokens; the oracle without rotation does not agree, so
+  the positions matter."""
   cfg = config([(sink_attn(heads=2, kv=1, dim=8, vdim=8, dims=8, base=7.0, scale=1.0, scaling=bands(3.0, 1.0, 4.0, 40)), None),
                 (cap_attn(heads=2, kv=1, dim=8, vdim=8, dims=8, base=5.0, scale=1.0, softcap=20.0, scaling=ramp(3.0, 4.0, 1.0, 30)), None)],
                width=32, vocab=50, groups=2)
   w = weights(cfg, seed=4)
   ids = toks(300, cfg["vocab"], seed=6)
   ref = logits(cfg, w, ids)
-  shifted = O.forward(cfg, w, ids, pos0=1)
-  assert rel(shifted[50:], ref[50:]) > 0.02
+  import copy
+  still = copy.deepcopy(cfg)
+  for lay in still["layers"]:
+    lay["mixer"]["rot"]["dims"] = 0
+  assert rel(logits(still, w, ids)[50:], ref[50:]) > 0.02
   st = stage(cfg, w, "float32", page=16)
   got = torch.cat([run(st, 0, ids[:130], 0), run(st, 0, ids[130:132], 130)] + [run(st, 0, [t], 132 + i) for i, t in enumerate(ids[132:])])
   st.close()
@@ -391,6 +394,82 @@ def test_bf16_prompt_equals_token_by_token(lib):
   st.close()
   assert rel(whole, ref) < TOL["bfloat16"] and rel(single, ref[150:]) < TOL["bfloat16"]
   assert rel(single, whole[150:]) < TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("kind,hd,heads,kv", [("attention", 64, 4, 2), ("attention_2", 64, 6, 2), ("attention", 128, 2, 1), ("attention_2", 128, 2, 2),
+                                              ("attention", 64, 8, 1)])
+def test_bf16_tensor_core_prompts_with_a_planted_key(lib, kind, hd, heads, kv):
+  """bf16 serving runs prompts through the tcgen05 attention (heads of 64 or 128): sink, score cap and, for mixed heads,
+  every query head against every key head's values.  A planted key at the borders of its 64-key tiles and of the query tiles,
+  in whole prompts, in portions that start inside a tile, against single tokens (the per-(token, head) kernel)."""
+  cfg, w = planted(kind, heads=heads, kv=kv, dim=hd, vdim=hd, dims=hd // 2, width=64)
+  st = stage(cfg, w, "bfloat16", page=16, cap=512)
+  n = 200
+  for at in (0, 63, 64, 65, 127, 128, 130):
+    ids = [(5 + 3 * i) % 48 + 2 for i in range(n)]
+    ids[at] = 1
+    ref = logits(cfg, w, ids)
+    before = st.counters()["tc_attention"]
+    whole = run(st, 0, ids, 0)
+    assert st.counters()["tc_attention"] > before
+    st.release_slot(0)
+    assert rel(whole, ref) < TOL["bfloat16"], (at, "prompt")
+    got = torch.cat([run(st, 0, ids[:70], 0), run(st, 0, ids[70:129], 70), run(st, 0, ids[129:131], 129)] +
+                    [run(st, 0, [t], 131 + i) for i, t in enumerate(ids[131:150])] + [run(st, 0, ids[150:], 150)])
+    st.release_slot(0)
+    assert rel(got, ref) < TOL["bfloat16"], (at, "portions")
+  ids2 = list(ids)
+  ids2[130] = 2
+  assert rel(logits(cfg, w, ids2)[131:], ref[131:]) > 3 * TOL["bfloat16"]     # the planted key shows
+  st.close()
+
+
+@pytest.mark.parametrize("kind,heads,kv", [("attention", 4, 2), ("attention_2", 8, 2), ("attention", 2, 1)])
+def test_bf16_split_key_decoding_with_a_far_key(lib, kind, heads, kv):
+  """Single tokens in bf16 serving run the split-key decode kernel: behind 680 tokens every (token, key head) shares its 64-key
+  tiles out over a cluster of blocks.  The planted key lies in the first, a middle and the newest tile, at tile borders."""
+  cfg, w = planted(kind, heads=heads, kv=kv, dim=64, vdim=64, dims=32, width=64)
+  st = stage(cfg, w, "bfloat16", page=16, cap=1024)
+  for at in (2, 63, 64, 319, 320, 671, 672, 679):
+    ids = [(5 + 3 * i) % 48 + 2 for i in range(700)]
+    ids[at] = 1
+    ref = logits(cfg, w, ids)
+    run(st, 1, ids[:680], 0, rows=[])
+    got = torch.cat([run(st, 1, [t], 680 + i) for i, t in enumerate(ids[680:])])
+    st.release_slot(1)
+    assert rel(got, ref[680:]) < TOL["bfloat16"], at
+  ids2 = list(ids)
+  ids2[679] = 2
+  assert rel(logits(cfg, w, ids2)[680:], ref[680:]) > 3 * TOL["bfloat16"]
+  # two sequences of unequal length in one step, through the captured graph of the serving call (last rows, no row list)
+  a, b = ids[:300], ids[:680]
+  st.forward([0, 2], [299, 679], [0, 0], tokens=torch.tensor(a[:-1] + b[:-1], dtype=torch.int32, device="cuda"), want_rows=[])
+  s = torch.cuda.Stream()
+  with torch.cuda.stream(s):
+    for rep in range(3):   # first call plans, second captures, third replays
+      if rep:
+        st.forward([0, 2], [299, 679], [0, 0], tokens=torch.tensor(a[:-1] + b[:-1], dtype=torch.int32, device="cuda"), want_rows=[])
+      last = st.forward([2, 0], [1, 1], [679, 299], tokens=torch.tensor([b[-1], a[-1]], dtype=torch.int32, device="cuda")).cpu().double()
+      assert rel(last[0:1], logits(cfg, w, b)[-1:]) < TOL["bfloat16"] and rel(last[1:2], logits(cfg, w, a)[-1:]) < TOL["bfloat16"], rep
+  st.close()
+
+
+def test_bf16_tensor_core_batch_of_unequal_prompts(lib):
+  """Rows of three requests in one step, query tiles cut per request; then one token of each."""
+  cfg = config([(cap_attn(heads=4, kv=2, dim=64, vdim=64, dims=32, softcap=3.0, scale=0.5), None), (sink_attn(heads=4, kv=2, dim=64, vdim=64, dims=64), None)],
+               width=128, vocab=50, groups=2)
+  w = weights(cfg, seed=23)
+  st = stage(cfg, w, "bfloat16", page=16, cap=512)
+  a, b, c = toks(70, 50, 7), toks(3, 50, 8), toks(129, 50, 9)
+  ra, rb, rc = (logits(cfg, w, x) for x in (a, b, c))
+  t1 = torch.tensor(a + b + c, dtype=torch.int32, device="cuda")
+  o1 = st.forward([0, 3, 1], [70, 3, 129], [0, 0, 0], tokens=t1, want_rows=list(range(202))).cpu().double()
+  assert st.counters()["tc_attention"] >= 2
+  assert rel(o1[:70], ra) < TOL["bfloat16"] and rel(o1[70:73], rb) < TOL["bfloat16"] and rel(o1[73:], rc) < TOL["bfloat16"]
+  nxt = st.forward([3, 0, 1], [1, 1, 1], [3, 70, 129], tokens=torch.tensor([b[0], a[0], c[0]], dtype=torch.int32, device="cuda")).cpu().double()
+  for row, seq in zip(nxt, (b + b[:1], a + a[:1], c + c[:1])):
+    assert rel(row[None], logits(cfg, w, seq)[-1:]) < TOL["bfloat16"]
+  st.close()
 
 
 # ----------------------------------------------------------------------------- the serving engine

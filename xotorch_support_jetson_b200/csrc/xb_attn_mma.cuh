@@ -50,7 +50,7 @@ __device__ __forceinline__ uint32_t att_tile_off(int r, int c16) {
 template <int HD, int NKB>
 __device__ __forceinline__ void att_warp_block(const uint32_t (*qf)[4], uint32_t sK, uint32_t sV, int krow0, int key_abs0,
                                                int lim0, int lim1, float scale_log2, float (&mrow)[2],
-                                               float (&lrow)[2], float (*o)[4]) {
+                                               float (&lrow)[2], float (*o)[4], float softcap = 0.f) {
   constexpr int KS = HD / 16;   // k-steps over the head dim
   constexpr int DT = HD / 8;    // output n-tiles over the head dim
   constexpr int NT = NKB * 2;   // score n-tiles (8 keys each)
@@ -77,7 +77,14 @@ __device__ __forceinline__ void att_warp_block(const uint32_t (*qf)[4], uint32_t
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
     const int k0 = kq + j * 8;
-    s[j][0] *= scale_log2; s[j][1] *= scale_log2; s[j][2] *= scale_log2; s[j][3] *= scale_log2;
+    if (softcap > 0.f) {
+      // cap * tanh(score / cap) in log2 units, tanh(x) = 1 - 2 / (1 + e^(2x))
+      const float ck = 2.0f * scale_log2 / softcap, cl = softcap * 1.4426950408889634f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[j][i] = cl * (1.0f - __fdividef(2.0f, 1.0f + exp2f(s[j][i] * ck)));
+    } else {
+      s[j][0] *= scale_log2; s[j][1] *= scale_log2; s[j][2] *= scale_log2; s[j][3] *= scale_log2;
+    }
     if (k0 > lim0) s[j][0] = -INFINITY;
     if (k0 + 1 > lim0) s[j][1] = -INFINITY;
     if (k0 > lim1) s[j][2] = -INFINITY;
@@ -129,7 +136,8 @@ __device__ __forceinline__ void att_warp_block(const uint32_t (*qf)[4], uint32_t
 // producer: stage one 64-key tile of K and V of kv head `kvh` (absolute tile index kt of the slot)
 template <int HD>
 __device__ __forceinline__ void att_issue_tile(const CUtensorMap* tmK, const CUtensorMap* tmV, uint8_t* sK, uint8_t* sV,
-                                               uint64_t* bar, const int* pt, int max_pages, int kt, int kvh, int KV, int P) {
+                                               uint64_t* bar, const int* pt, int max_pages, int kt, int kvh, int KV, int P,
+                                               int v_wide = 0, int vh = 0) {
   constexpr int TILE_BYTES = XB_ATT_TILE * HD * 2;
   mbar_expect_tx(bar, 2 * TILE_BYTES);
   const int BR = P < XB_ATT_TILE ? P : XB_ATT_TILE;   // rows per TMA box
@@ -138,10 +146,12 @@ __device__ __forceinline__ void att_issue_tile(const CUtensorMap* tmK, const CUt
     const int pi = key / P;
     const int page = pt[pi < max_pages ? pi : max_pages - 1];   // rows past the context are masked
     const int row = (page * KV + kvh) * P + (key % P);
+    // v_wide: a value row holds every key head's values side by side; this block reads head vh of it
+    const int vrow = v_wide ? page * P + (key % P) : row, vx0 = v_wide ? vh * HD : 0;
 #pragma unroll
     for (int db = 0; db < HD / 64; ++db) {
       tma_load_2d(sK + db * (XB_ATT_TILE * 128) + rg * BR * 128, tmK, bar, db * 64, row);
-      tma_load_2d(sV + db * (XB_ATT_TILE * 128) + rg * BR * 128, tmV, bar, db * 64, row);
+      tma_load_2d(sV + db * (XB_ATT_TILE * 128) + rg * BR * 128, tmV, bar, vx0 + db * 64, vrow);
     }
   }
 }
@@ -166,6 +176,16 @@ struct AttDecCfg {
 // attention block finishes the q rows of its own head group and -- in the block that holds the newest tile --
 // the step's k / v row (bias, bf16 rounding, RoPE; arithmetic of xb_qkv_finalize_kernel), appends that row to
 // the paged cache and uses it from shared memory: one launch and one dependency hop less per layer.
+// Options of the decode kernel beyond plain causal attention (all zero = none): a sink per head in the softmax denominator,
+// a cap on the scores, wide value rows (grid y = KV * KV: block y reads keys of head y % KV and values of head y / KV and
+// writes to out + (token * H + head) * out_head_stride + (y / KV) * HD; out_head_stride 0 = HD).  With wide value rows the
+// splits are merged inside a cluster or not made at all (the global partial buffers are not laid out for them).
+struct AttDecOpt {
+  const float* sink;
+  float softcap;
+  int v_wide;
+  long long out_head_stride;
+};
 struct QkvFin {
   const float* part;
   SplitInfo si;
@@ -180,7 +200,7 @@ template <int HD, int G, int NST, bool FUSED>
 __global__ void __launch_bounds__(160) xb_attn_decode_mma_kernel(
     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const bf16* __restrict__ q,
     BatchMeta m, float* __restrict__ o_part, float* __restrict__ ml_part, bf16* __restrict__ out, int H, int KV,
-    int n_splits, float scale_log2, QkvFin f, int cluster_merge) {
+    int n_splits, float scale_log2, QkvFin f, int cluster_merge, AttDecOpt opt) {
   namespace cg = cooperative_groups;
   using Cfg = AttDecCfg<HD, G, NST>;
   extern __shared__ uint8_t smem_raw[];
@@ -196,7 +216,9 @@ __global__ void __launch_bounds__(160) xb_attn_decode_mma_kernel(
   bf16* sKrow = sQ + G * HD;                                              // [HD]
   bf16* sVrow = sKrow + HD;                                               // [HD]
 
-  const int t = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
+  const int t = blockIdx.x, kvh = opt.v_wide ? (int)blockIdx.y % KV : (int)blockIdx.y, sp = blockIdx.z;
+  const int vh = opt.v_wide ? (int)blockIdx.y / KV : 0;
+  const long long ohs = opt.out_head_stride > 0 ? opt.out_head_stride : (long long)HD;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
   // The batch metadata and page table were uploaded before the step's first kernel started, and
@@ -238,7 +260,7 @@ __global__ void __launch_bounds__(160) xb_attn_decode_mma_kernel(
         }
         mbar_wait(&empty_bar[stage], phase ^ 1);
         uint8_t* sK = stages + stage * Cfg::STAGE_BYTES;
-        att_issue_tile<HD>(&tmK, &tmV, sK, sK + Cfg::TILE_BYTES, &full_bar[stage], pt, m.max_pages, kt, kvh, KV, m.page_tokens);
+        att_issue_tile<HD>(&tmK, &tmV, sK, sK + Cfg::TILE_BYTES, &full_bar[stage], pt, m.max_pages, kt, kvh, KV, m.page_tokens, opt.v_wide, vh);
         if (++stage == NST) { stage = 0; phase ^= 1; }
       }
     }
@@ -316,7 +338,7 @@ __global__ void __launch_bounds__(160) xb_attn_decode_mma_kernel(
       }
       if (key_abs0 + warp * 16 <= pos) {
         const uint32_t sK = smem_u32(stages + stage * Cfg::STAGE_BYTES);
-        att_warp_block<HD, 1>(qf, sK, sK + Cfg::TILE_BYTES, warp * 16, key_abs0, pos, pos, scale_log2, mrow, lrow, o);
+        att_warp_block<HD, 1>(qf, sK, sK + Cfg::TILE_BYTES, warp * 16, key_abs0, pos, pos, scale_log2, mrow, lrow, o, opt.softcap);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[stage]);
@@ -357,7 +379,8 @@ __global__ void __launch_bounds__(160) xb_attn_decode_mma_kernel(
       }
       const int hh = kvh * G + g;
       if (n_splits == 1) {
-        out[((long long)t * H + hh) * HD + d] = f2bf(L > 0.f ? A / L : 0.f);
+        if (opt.sink != nullptr && M > -INFINITY) L += exp2f(opt.sink[hh] * 1.4426950408889634f - M);
+        out[((long long)t * H + hh) * ohs + (long long)vh * HD + d] = f2bf(L > 0.f ? A / L : 0.f);
       } else if (cluster_merge) {
         xc_o[idx] = A;
         if (d == 0) { xc_ml[g * 2] = M; xc_ml[g * 2 + 1] = L; }       // M in log2 units
@@ -385,7 +408,8 @@ __global__ void __launch_bounds__(160) xb_attn_decode_mma_kernel(
         }
         const float M = warp_max(ms);
         const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-        const float L = warp_sum(ls * w);
+        float L = warp_sum(ls * w);
+        if (opt.sink != nullptr && M > -INFINITY) L += exp2f(opt.sink[kvh * G + g] * 1.4426950408889634f - M);
         constexpr int VPL = HD / 32;
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int s0 = 0; s0 < n_splits; s0 += 8) {
@@ -409,7 +433,7 @@ __global__ void __launch_bounds__(160) xb_attn_decode_mma_kernel(
           }
         }
         const float invL = L > 0.f ? 1.0f / L : 0.f;
-        bf16* dst = out + ((long long)t * H + kvh * G + g) * HD + lane * VPL;
+        bf16* dst = out + ((long long)t * H + kvh * G + g) * ohs + (long long)vh * HD + lane * VPL;
 #pragma unroll
         for (int j = 0; j < VPL; j += 2)
           *reinterpret_cast<uint32_t*>(dst + j) = f2_to_bf2(acc[j] * invL, acc[j + 1] * invL);
@@ -537,11 +561,20 @@ struct AttMask {
 // Where the query rows come from and what the epilogue does besides the normalisation.  q row of (token t, head h):
 // q + t * ldq + h * HD (+ qbias[h * HD + .] added in fp32 before the bf16 rounding when qbias != nullptr);
 // gate != nullptr: the output is multiplied by sigmoid(gate[t * ld_gate + h * HD + .]).
+// sink != nullptr: exp(sink[head]) joins the softmax denominator (no key, no value).  softcap > 0: the scaled score s becomes
+// cap * tanh(s / cap) before the softmax.  v_wide: a row of the value pool holds every key head's values side by side
+// ([page][token][KV * HD]); block z then reads value head z whatever its key head is and writes to
+// out + (token * H + head) * out_head_stride + z * HD, so that every query head meets every value head (grid z = KV).
+// out_head_stride 0 = HD.
 struct AttIo {
   long long ldq;
   const float* qbias;
   const bf16* gate;
   long long ld_gate;
+  const float* sink;
+  float softcap;
+  int v_wide;
+  long long out_head_stride;
 };
 
 template <int HD, int G>
@@ -644,17 +677,18 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
     if (lane == 0) {
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
-      auto issue = [&](const CUtensorMap* tm, uint8_t* dst, uint64_t* bar, int kt) {
+      auto issue = [&](const CUtensorMap* tm, uint8_t* dst, uint64_t* bar, int kt, bool wide = false) {
         mbar_expect_tx(bar, Cfg::TILE_BYTES);
+        const int x0 = wide ? (int)blockIdx.z * HD : 0;
         for (int rg = 0; rg < rgs; ++rg) {
           const int i = kt * rgs + rg;
           const int key = tile_of(kt) * XB_ATT_TILE + rg * BR;
           int page;
           if (i < XB_ATT_PG_CACHE) page = s_pages[i];
           else { const int pi = key / P; page = pt[pi < m.max_pages ? pi : m.max_pages - 1]; }
-          const int row = (page * KV + kvh) * P + (key % P);
+          const int row = wide ? page * P + (key % P) : (page * KV + kvh) * P + (key % P);
 #pragma unroll
-          for (int db = 0; db < HD / 64; ++db) tma_load_2d(dst + db * (XB_ATT_TILE * 128) + rg * BR * 128, tm, bar, db * 64, row);
+          for (int db = 0; db < HD / 64; ++db) tma_load_2d(dst + db * (XB_ATT_TILE * 128) + rg * BR * 128, tm, bar, x0 + db * 64, row);
         }
       };
       auto issue_k = [&](int kt) {
@@ -668,7 +702,7 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
         if (kt + 1 < n_kt) issue_k(kt + 1);
         const int vs = kt % Cfg::NST;
         mbar_wait(&v_empty[vs], ((kt / Cfg::NST) & 1) ^ 1);
-        issue(&tmV, sVr + vs * Cfg::TILE_BYTES, &v_full[vs], kt);
+        issue(&tmV, sVr + vs * Cfg::TILE_BYTES, &v_full[vs], kt, io.v_wide != 0);
       }
     }
   } else if (warp == 1) {
@@ -753,6 +787,8 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
     }
     float m_used = -INFINITY;     // reference max (scaled, log2 units) that O and l are expressed against
     float l_sum = 0.f;
+    const float sl2 = io.softcap > 0.f ? 1.4426950408889634f : scale_log2;       // what turns a score in v[] into log2 units
+    const float cap_k = io.softcap > 0.f ? 2.0f * scale_log2 / io.softcap : 0.f;  // raw product -> 2 s / cap in log2 units
     for (int kt = 0; kt < n_kt; ++kt) {
       mbar_wait(&s_full[kt & 1], (kt >> 1) & 1);
       tc_fence_after();
@@ -763,6 +799,16 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
 #pragma unroll
       for (int c = 0; c < XB_ATT_TILE; c += 16) tmem_ld16(tm_Sk + lane_base + c, v + c);
       tmem_ld_wait();
+      if (io.softcap > 0.f) {
+        // capped score cap * tanh(s / cap) in place of the raw product, tanh(x) = 1 - 2 / (1 + e^(2x)); the softmax below
+        // then works on natural-log scores (sl2 = log2 e)
+#pragma unroll
+        for (int j = 0; j < XB_ATT_TILE; ++j) {
+          float ex;
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(__uint_as_float(v[j]) * cap_k));
+          v[j] = __float_as_uint(io.softcap * (1.0f - __fdividef(2.0f, 1.0f + ex)));
+        }
+      }
       // only tiles that reach past the first row's position, or (with a window) back beyond the last row's window,
       // need per-element masks.  The row sees key k when k <= lim and (k >= lo_row or k < kf).
       const bool masked = key0 + XB_ATT_TILE - 1 > pos0 || (mk.window > 0 && last_pos - key0 >= mk.window);
@@ -778,7 +824,7 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
 #pragma unroll
         for (int j = 0; j < XB_ATT_TILE; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(v[j]));
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;   // scale > 0
 #if !XB_ATT_P_TMEM
       // ---- the (single) P buffer was last read by PV of tile kt-1
       if (kt > 0) {
@@ -823,7 +869,7 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
         float p[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p[j]) : "f"(fmaf(__uint_as_float(v[c + j]), scale_log2, nmref)));
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p[j]) : "f"(fmaf(__uint_as_float(v[c + j]), sl2, nmref)));
         if (masked) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
@@ -855,8 +901,10 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
     // ---- epilogue: O / l -> bf16 -> attention output row
     mbar_wait(&o_done[(n_kt - 1) & 1], ((n_kt - 1) >> 1) & 1);
     tc_fence_after();
+    if (io.sink != nullptr && m_used != -INFINITY) l_sum += exp2f(io.sink[kvh * G + gq] * 1.4426950408889634f - m_used);
     const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
-    bf16* dst = out + ((long long)(t0 + (valid ? tq : 0)) * H + (kvh * G + gq)) * HD;
+    const long long ohs = io.out_head_stride > 0 ? io.out_head_stride : (long long)HD;
+    bf16* dst = out + ((long long)(t0 + (valid ? tq : 0)) * H + (kvh * G + gq)) * ohs + (io.v_wide ? (long long)blockIdx.z * HD : 0);
     const bf16* gate = io.gate != nullptr ? io.gate + (long long)(t0 + (valid ? tq : 0)) * io.ld_gate + (long long)(kvh * G + gq) * HD : nullptr;
 #pragma unroll 1
     for (int c = 0; c < HD; c += 16) {

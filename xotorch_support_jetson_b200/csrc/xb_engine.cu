@@ -43,6 +43,7 @@ static void hy_destroy(HyModel* hy);
 static int hy_reserve(xb_engine* e);
 static int hy_finalize(xb_engine* e);
 static void hy_drop_plans(xb_engine* e);
+static int hy_kv_splits(xb_engine* e, int T, int max_ctx);
 static int hy_missing(xb_engine* e, char* buf, size_t buflen, int* n_missing);
 static int hy_load_file(xb_engine* e, const char* path, const std::vector<StEntry>& entries, const uint8_t* data, size_t data_size,
                         int* n_tensors, uint64_t* n_bytes);
@@ -827,7 +828,7 @@ static int launch_attn_decode(xb_engine* e, const LayerW& w, const BatchMeta& m,
   }
   dim3 grid(T, d.n_kv_heads, n_splits);
   XB_TRY(launch_kc(e, kern, grid, dim3(160), Cfg::SMEM_BYTES, st, dim3(1, 1, cl ? n_splits : 1), w.tmK, w.tmV, e->q, m, e->o_part,
-                   e->ml_part, e->attn, d.n_heads, d.n_kv_heads, n_splits, scale_log2, fin, cl));
+                   e->ml_part, e->attn, d.n_heads, d.n_kv_heads, n_splits, scale_log2, fin, cl, AttDecOpt{nullptr, 0.f, 0, 0}));
   if (n_splits > 1 && !cl) {
     const int rows = T * d.n_heads;
     XB_TRY(launch_k(e, xb_attn_combine2_kernel<HD>, dim3((rows + 3) / 4), dim3(128), 0, st, 1, e->o_part, e->ml_part, e->attn, n_splits, rows));
@@ -957,7 +958,7 @@ static void fill_batch_meta(const xb_engine* e, BatchMeta& m) {
 
 static int run_body(xb_engine* e, int T, int n_seqs, int n_splits, int n_tiles, void* const* taps, cudaStream_t st,
                     int ho_in = 0, int ho_out = 0, int with_head = 1) {
-  if (e->hy != nullptr) return hy_run_body(e, T, n_seqs, n_tiles, taps, st, with_head);
+  if (e->hy != nullptr) return hy_run_body(e, T, n_seqs, n_splits, n_tiles, taps, st, with_head);
   const xb_model_desc& d = e->d;
   const bool first = shard_is_first(d), last = shard_is_last(d);
   BatchMeta m;
@@ -1195,6 +1196,8 @@ static int forward_impl(xb_engine* e, const xb_batch* b, void* out, void* const*
   int n_splits = 1;
   if (decode_only && e->hy == nullptr) {
     n_splits = choose_kv_splits(e, T, max_ctx);   // 1 once T * kv heads exceeds one wave (no split workspace needed)
+  } else if (decode_only) {
+    n_splits = hy_kv_splits(e, T, max_ctx);       // attention layers of a hybrid model that decode through the same kernel
   }
 
   if (e->sel_rows != nullptr && e->sel_n > 0)

@@ -80,6 +80,7 @@ struct HyModel {
   size_t maxQA = 0, maxE = 0, maxM = 0;   // maxM: widest matrix that passes through the m1 / m2 buffers besides the stream's width
   float* vfirst = nullptr;              // values of the first blending layer for the tokens of this step [T, G * dv]
   size_t maxGV = 0;
+  int dec_splits = 1;                   // key splits of this step's single-token attention (hy_kv_splits)
   bool pdl_now = false;
   int recur_lpc = 0;         // XB_HY_LPC=4|8|16 pins the lanes per state column (A/B); 0: by the step's shape
   int use_tc_attn = 1;       // XB_HY_TC_ATTN=0: attention through the per-token kernel everywhere (A/B)
@@ -303,6 +304,10 @@ static int hy_create_softmax(xb_engine* e, int i, bool own, uint64_t& wbytes, ui
   if (qa > hy->maxQA) hy->maxQA = qa;
   if (ol > hy->maxO) hy->maxO = ol;
   if (c.s_vmix && (size_t)(G * dv) > hy->maxGV) hy->maxGV = (size_t)(G * dv);
+  // bf16 serving, key and value heads of one size (64 or 128), at most 8 query heads per key head: prompts run through the
+  // engine's tcgen05 attention (sink, score cap and the wide value rows of mixed heads as its options)
+  l.tc_attn = !d.compute_fp32 && dk == dv && (dk == 64 || dk == 128) && H / G <= 8;
+  if (l.tc_attn && qa > hy->maxQG) hy->maxQG = qa;
   wbytes += ((size_t)l.n_in * D + D * l.n_o) * 2;
   kvpos += (uint64_t)G * (dk + dv) * (d.compute_fp32 ? 4 : 2);
   return 0;
@@ -736,6 +741,13 @@ static int hy_reserve(xb_engine* e) {
       XB_TRY(dmalloc(&l.v_pool, vb));
       XB_CUDA(cudaMemset(l.k_pool, 0, kb));
       XB_CUDA(cudaMemset(l.v_pool, 0, vb));
+      if (l.tc_attn) {
+        const long long G = l.d.s_kv_heads, pool_rows = (long long)e->n_pages * G * e->page_tokens;
+        const int box_rows = e->page_tokens < 64 ? e->page_tokens : 64;
+        XB_TRY(xb_make_tmap(&l.tmK, l.k_pool, pool_rows, l.d.s_dim, l.d.s_dim, box_rows));
+        if (l.v_all) XB_TRY(xb_make_tmap(&l.tmV, l.v_pool, pool_rows / G, G * l.d.s_vdim, G * l.d.s_vdim, box_rows));
+        else XB_TRY(xb_make_tmap(&l.tmV, l.v_pool, pool_rows, l.d.s_vdim, l.d.s_vdim, box_rows));
+      }
       continue;
     }
     if (l.d.mixer != XB_MIX_PARALLEL) continue;
@@ -766,8 +778,9 @@ static int hy_tile_tokens(const xb_hybrid_desc& d, const xb_hybrid_layer* layers
   int tt = 128;
   for (int i = 0; i < d.n_layers; ++i) {
     const xb_hybrid_layer& c = layers[i];
-    if (c.mixer != XB_MIX_PARALLEL || c.a_kv_heads <= 0 || c.a_heads % c.a_kv_heads != 0) continue;
-    const int group = c.a_heads / c.a_kv_heads;
+    int group = 0;
+    if (c.mixer == XB_MIX_PARALLEL && c.a_kv_heads > 0 && c.a_heads % c.a_kv_heads == 0) group = c.a_heads / c.a_kv_heads;
+    if (c.mixer == XB_MIX_SOFTMAX && c.s_kv_heads > 0 && c.s_heads % c.s_kv_heads == 0) group = c.s_heads / c.s_kv_heads;
     if (group >= 1 && group <= 8 && 128 / group < tt) tt = 128 / group;
   }
   return tt;
@@ -946,6 +959,61 @@ static int hy_attn_tc(xb_engine* e, const HyLayer& l, const BatchMeta& m, const 
     case 8: return hy_attn_tc_g<HD, 8>(e, l, m, in, out, st);
   }
   return xb_fail(1, "no tcgen05 attention for %d query heads per key head", l.d.a_heads / l.d.a_kv_heads);
+}
+
+// the tcgen05 prompt attention for any layer kind: H query / KV key heads, grid z blocks per (tile, key head)
+template <int HD, int GRP>
+static int hy_attn_tc_any_g(xb_engine* e, const HyLayer& l, const BatchMeta& m, const HyAttnIn& in, bf16* out, int H, int KV, float scale, int gz,
+                            cudaStream_t st) {
+  using Cfg = AttTcCfg<HD>;
+  XB_SMEM_ATTR_ONCE((xb_attn_prefill_tc_kernel<HD, GRP>), Cfg::SMEM_BYTES);
+  e->c.tc_attention++;
+  return hy_launch(e, xb_attn_prefill_tc_kernel<HD, GRP>, dim3(in.n_tiles, KV, gz), dim3(192), Cfg::SMEM_BYTES, st, l.tmK, l.tmV, in.q, m,
+                   in.tile_start, in.tile_len, out, H, KV, scale * 1.4426950408889634f, AttMask{0, 0}, in.io);
+}
+template <int HD>
+static int hy_attn_tc_any(xb_engine* e, const HyLayer& l, const BatchMeta& m, const HyAttnIn& in, bf16* out, int H, int KV, float scale, int gz,
+                          cudaStream_t st) {
+  switch (H / KV) {
+    case 1: return hy_attn_tc_any_g<HD, 1>(e, l, m, in, out, H, KV, scale, gz, st);
+    case 2: return hy_attn_tc_any_g<HD, 2>(e, l, m, in, out, H, KV, scale, gz, st);
+    case 3: return hy_attn_tc_any_g<HD, 3>(e, l, m, in, out, H, KV, scale, gz, st);
+    case 4: return hy_attn_tc_any_g<HD, 4>(e, l, m, in, out, H, KV, scale, gz, st);
+    case 5: return hy_attn_tc_any_g<HD, 5>(e, l, m, in, out, H, KV, scale, gz, st);
+    case 6: return hy_attn_tc_any_g<HD, 6>(e, l, m, in, out, H, KV, scale, gz, st);
+    case 7: return hy_attn_tc_any_g<HD, 7>(e, l, m, in, out, H, KV, scale, gz, st);
+    case 8: return hy_attn_tc_any_g<HD, 8>(e, l, m, in, out, H, KV, scale, gz, st);
+  }
+  return xb_fail(1, "no tcgen05 attention for %d query heads per key head", H / KV);
+}
+
+// A step of single tokens through the engine's split-key decode attention (mma.sync over TMA-staged tiles, the splits of a
+// (token, key head) merged inside a thread-block cluster), with the sink / cap / wide-value options of the layer.
+template <int HD, int GRP>
+static int hy_attn_dec_g(xb_engine* e, const HyLayer& l, const BatchMeta& m, int T, const bf16* q, bf16* out, int H, int KV, float scale,
+                         int n_splits, const AttDecOpt& opt, cudaStream_t st) {
+  constexpr int NST = 3;
+  using Cfg = AttDecCfg<HD, GRP, NST>;
+  auto kern = xb_attn_decode_mma_kernel<HD, GRP, NST, false>;
+  XB_SMEM_ATTR_ONCE(kern, Cfg::SMEM_BYTES);
+  const dim3 grid(T, opt.v_wide ? KV * KV : KV, n_splits);
+  return launch_kc(e, kern, grid, dim3(160), Cfg::SMEM_BYTES, st, dim3(1, 1, n_splits), l.tmK, l.tmV, q, m, (float*)nullptr, (float*)nullptr, out,
+                   H, KV, n_splits, scale * 1.4426950408889634f, QkvFin{}, n_splits > 1 ? 1 : 0, opt);
+}
+template <int HD>
+static int hy_attn_dec(xb_engine* e, const HyLayer& l, const BatchMeta& m, int T, const bf16* q, bf16* out, int H, int KV, float scale,
+                       int n_splits, const AttDecOpt& opt, cudaStream_t st) {
+  switch (H / KV) {
+    case 1: return hy_attn_dec_g<HD, 1>(e, l, m, T, q, out, H, KV, scale, n_splits, opt, st);
+    case 2: return hy_attn_dec_g<HD, 2>(e, l, m, T, q, out, H, KV, scale, n_splits, opt, st);
+    case 3: return hy_attn_dec_g<HD, 3>(e, l, m, T, q, out, H, KV, scale, n_splits, opt, st);
+    case 4: return hy_attn_dec_g<HD, 4>(e, l, m, T, q, out, H, KV, scale, n_splits, opt, st);
+    case 5: return hy_attn_dec_g<HD, 5>(e, l, m, T, q, out, H, KV, scale, n_splits, opt, st);
+    case 6: return hy_attn_dec_g<HD, 6>(e, l, m, T, q, out, H, KV, scale, n_splits, opt, st);
+    case 7: return hy_attn_dec_g<HD, 7>(e, l, m, T, q, out, H, KV, scale, n_splits, opt, st);
+    case 8: return hy_attn_dec_g<HD, 8>(e, l, m, T, q, out, H, KV, scale, n_splits, opt, st);
+  }
+  return xb_fail(1, "no decode attention for %d query heads per key head", H / KV);
 }
 
 template <typename AT>
@@ -1175,7 +1243,7 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
 // projection reads.  Rotation, value blending and the cache append are one kernel; the attention runs a block per
 // (token, head) over the pages; mixed heads / head gates follow in a kernel of their own.
 template <typename AT>
-static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, const LinOut& P, const BatchMeta& m, cudaStream_t st) {
+static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, int n_tiles, const LinOut& P, const BatchMeta& m, cudaStream_t st) {
   HyModel* hy = e->hy;
   const xb_hybrid_layer& c = l.d;
   typedef typename std::conditional<std::is_same<AT, float>::value, float, bf16>::type KT;
@@ -1184,11 +1252,41 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, c
   RotArgs r;
   r.freq = l.rot_freq_d; r.dims = c.s_rot_dims; r.half = c.s_rot_pairs == XB_ROPE_HALF_SPLIT ? 1 : 0; r.mult = c.s_rot_mult;
   const int units = (H + G) * (dk - c.s_rot_dims / 2) + G * dv;
+  // prompts in bf16 serving at the head sizes it takes: the tcgen05 kernel over the step's query tiles
+  const bool tc = std::is_same<AT, bf16>::value && l.tc_attn && hy->use_tc_attn && n_tiles > 0;
+  // steps of single tokens, same sizes: the split-key decode kernel (its splits merge inside a cluster)
+  const bool dec = std::is_same<AT, bf16>::value && l.tc_attn && hy->use_tc_attn && n_tiles == 0 && T == n_seqs && e->attn_cluster != 0;
   XB_TRY(hy_launch(e, hy_rope_append_kernel<KT>, dim3(T, (units + 255) / 256), dim3(256), 0, st, P, l.off_q, l.off_k, l.off_v, H, G, dk, dv, r,
-                   hy->qa, (KT*)l.k_pool, (KT*)l.v_pool, l.v_all ? 1 : 0, (const float*)l.vmix, hy->vfirst, l.vmode, m));
+                   hy->qa, (tc || dec) ? hy->qg : (bf16*)nullptr, (KT*)l.k_pool, (KT*)l.v_pool, l.v_all ? 1 : 0, (const float*)l.vmix, hy->vfirst,
+                   l.vmode, m));
   const int dvo = l.v_all ? G * dv : dv;
   const AttnOpt opt{c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : G};
   const bool post = c.s_talk != 0 || c.s_gate != 0;
+  if (dec) {
+    // mixed heads multiply the blocks by the key heads: fewer splits keep the grid near one wave
+    int ns = l.v_all ? hy->dec_splits / G : hy->dec_splits;
+    ns = ns < 1 ? 1 : ns;
+    const AttDecOpt dopt{c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : 0, (long long)dvo};
+    bf16* dst = post ? reinterpret_cast<bf16*>(hy->o) : reinterpret_cast<bf16*>(hy->a1);
+    if (dk == 128) XB_TRY(hy_attn_dec<128>(e, l, m, T, hy->qg, dst, H, G, c.s_scale, ns, dopt, st));
+    else XB_TRY(hy_attn_dec<64>(e, l, m, T, hy->qg, dst, H, G, c.s_scale, ns, dopt, st));
+    if (post)
+      XB_TRY(hy_launch(e, hy_heads_mix_kernel<AT, bf16>, dim3(T, (H * dv + 255) / 256), dim3(256), 0, st, (const bf16*)hy->o,
+                       c.s_talk ? (const float*)l.talk : (const float*)nullptr, P, c.s_gate ? l.off_g : -1, H, l.v_all ? G : 1, dv, a1, (long long)l.n_o));
+    return 0;
+  }
+  if (tc) {
+    HyAttnIn in;
+    in.tile_start = m.tile_start; in.tile_len = m.tile_len; in.n_tiles = n_tiles; in.q = hy->qg;
+    in.io = AttIo{(long long)H * dk, nullptr, nullptr, 0, c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : 0, (long long)dvo};
+    bf16* dst = post ? reinterpret_cast<bf16*>(hy->o) : reinterpret_cast<bf16*>(hy->a1);
+    if (dk == 128) XB_TRY(hy_attn_tc_any<128>(e, l, m, in, dst, H, G, c.s_scale, l.v_all ? G : 1, st));
+    else XB_TRY(hy_attn_tc_any<64>(e, l, m, in, dst, H, G, c.s_scale, l.v_all ? G : 1, st));
+    if (post)
+      XB_TRY(hy_launch(e, hy_heads_mix_kernel<AT, bf16>, dim3(T, (H * dv + 255) / 256), dim3(256), 0, st, (const bf16*)hy->o,
+                       c.s_talk ? (const float*)l.talk : (const float*)nullptr, P, c.s_gate ? l.off_g : -1, H, l.v_all ? G : 1, dv, a1, (long long)l.n_o));
+    return 0;
+  }
   const int aw = 16, far = 1 << 30;   // causal over the whole sequence: the block's warps share out all earlier keys
   const size_t asm_bytes = (size_t)(((dk + 3) & ~3) + aw * (2 + dvo)) * sizeof(float);
   const LinOut Q = hy_plain(hy->qa, (long long)H * dk);
@@ -1202,7 +1300,7 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, c
     else
       XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 16>, grid, block, asm_bytes, st, Q, 0, -1, kp, vp, m, H, G, dk, dvo, dk, dvo, far, 0,
                        c.s_scale, 1.0f, hy->o, (long long)H * dvo, opt));
-    XB_TRY(hy_launch(e, hy_heads_mix_kernel<AT>, dim3(T, (H * dv + 255) / 256), dim3(256), 0, st, (const float*)hy->o,
+    XB_TRY(hy_launch(e, hy_heads_mix_kernel<AT, float>, dim3(T, (H * dv + 255) / 256), dim3(256), 0, st, (const float*)hy->o,
                      c.s_talk ? (const float*)l.talk : (const float*)nullptr, P, c.s_gate ? l.off_g : -1, H, l.v_all ? G : 1, dv, a1, (long long)l.n_o));
   } else {
     if (dvo <= 256)
@@ -1265,7 +1363,7 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
                        (const float*)l.head_norm, P, l.off_g, d.norm_eps, 1.0f, a1, (long long)l.n_o, H, dv, 0, 0));
       XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
     } else if (c.mixer == XB_MIX_SOFTMAX) {
-      XB_TRY(hy_softmax_mixer<AT>(e, l, T, n_seqs, P, m, st));
+      XB_TRY(hy_softmax_mixer<AT>(e, l, T, n_seqs, n_tiles, P, m, st));
       XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
     } else {
       const int H = c.a_heads, G = c.a_kv_heads, dk = c.a_dim, dv = c.a_vdim;
@@ -1371,7 +1469,23 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
   return 0;
 }
 
-static int hy_run_body(xb_engine* e, int T, int n_seqs, int n_tiles, void* const* taps, cudaStream_t st, int with_head) {
+static int hy_run_body(xb_engine* e, int T, int n_seqs, int n_splits, int n_tiles, void* const* taps, cudaStream_t st, int with_head) {
+  e->hy->dec_splits = n_splits > 0 ? n_splits : 1;
   if (e->hy->d.compute_fp32) return hy_run_body_t<float>(e, T, n_seqs, n_tiles, taps, st, with_head);
   return hy_run_body_t<bf16>(e, T, n_seqs, n_tiles, taps, st, with_head);
+}
+
+// Key splits of a step of single tokens for the attention layers that decode through the split-key tensor-core kernel: one
+// wave of about two blocks per SM over (token, key head, split), at most one cluster of splits; 1 when no layer uses it.
+static int hy_kv_splits(xb_engine* e, int T, int max_ctx) {
+  HyModel* hy = e->hy;
+  int kv = 0;
+  for (const HyLayer& l : hy->L)
+    if (l.d.mixer == XB_MIX_SOFTMAX && l.tc_attn && l.d.s_kv_heads > kv) kv = l.d.s_kv_heads;
+  if (kv == 0 || !e->attn_cluster || !hy->use_tc_attn) return 1;
+  const int tiles = (max_ctx + XB_ATT_TILE - 1) / XB_ATT_TILE;
+  int n = (2 * e->num_sms) / (T * kv);
+  n = n > 8 ? 8 : n;
+  n = n > tiles ? tiles : n;
+  return n < 1 ? 1 : n;
 }

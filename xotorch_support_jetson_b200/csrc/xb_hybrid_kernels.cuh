@@ -1061,13 +1061,14 @@ __device__ __forceinline__ void hy_rot_cs(const RotArgs& r, int pos, int i, floa
   *s *= r.mult;
 }
 // One token row of an XB_MIX_SOFTMAX layer after its input projection P = [q | k | v | ...]: rotated queries -> qa (fp32
-// [T, H * dk]), rotated keys -> the key pool, values -> the value pool.  vmode 1: the values are also left in vfirst
+// [T, H * dk], or bf16 q16 when given: what the tensor-core attention reads), rotated keys -> the key pool, values -> the
+// value pool.  vmode 1: the values are also left in vfirst
 // ([T, G * dv] fp32) for later layers of the step; vmode 2: v <- (1 - l) v + l vfirst with l = vmix[0] before they are
 // cached.  v_all: a value row holds all G heads ([page][token][G * dv]) instead of [page][G][token][dv].
 // A thread owns a rotating pair or one entry that does not turn.  grid (T, ceil(units / 256)).
 template <typename KT>
 __global__ void __launch_bounds__(256) hy_rope_append_kernel(LinOut P, int off_q, int off_k, int off_v, int H, int G, int dk, int dv,
-                                                             RotArgs r, float* __restrict__ qa, KT* __restrict__ k_pool,
+                                                             RotArgs r, float* __restrict__ qa, bf16* __restrict__ q16, KT* __restrict__ k_pool,
                                                              KT* __restrict__ v_pool, int v_all, const float* __restrict__ vmix,
                                                              float* __restrict__ vfirst, int vmode, BatchMeta m) {
   pdl_launch_dependents();
@@ -1084,7 +1085,7 @@ __global__ void __launch_bounds__(256) hy_rope_append_kernel(LinOut P, int off_q
       const bool is_q = hd < H;
       const int h = is_q ? hd : hd - H;
       const int src = (is_q ? off_q : off_k) + h * dk;
-      float* qo = qa + (long long)row * H * dk + (long long)h * dk;
+      const long long qi = (long long)row * H * dk + (long long)h * dk;
       KT* ko = k_pool + ((page * G + h) * m.page_tokens + in_page) * dk;
       if (j < hp) {
         const int d0 = r.half ? j : 2 * j, d1 = r.half ? j + hp : 2 * j + 1;
@@ -1092,13 +1093,15 @@ __global__ void __launch_bounds__(256) hy_rope_append_kernel(LinOut P, int off_q
         float c, sn;
         hy_rot_cs(r, pos, j, &c, &sn);
         const float y0 = a * c - b * sn, y1 = b * c + a * sn;
-        if (is_q) { qo[d0] = y0; qo[d1] = y1; }
-        else { act_store<KT>(ko + d0, y0); act_store<KT>(ko + d1, y1); }
+        if (!is_q) { act_store<KT>(ko + d0, y0); act_store<KT>(ko + d1, y1); }
+        else if (q16 != nullptr) { q16[qi + d0] = f2bf(y0); q16[qi + d1] = f2bf(y1); }
+        else { qa[qi + d0] = y0; qa[qi + d1] = y1; }
       } else {
         const int d = r.dims + (j - hp);
         const float a = lin_at(P, row, src + d);
-        if (is_q) qo[d] = a;
-        else act_store<KT>(ko + d, a);
+        if (!is_q) act_store<KT>(ko + d, a);
+        else if (q16 != nullptr) q16[qi + d] = f2bf(a);
+        else qa[qi + d] = a;
       }
     } else {
       const int i = u - n_qk;
@@ -1118,8 +1121,8 @@ __global__ void __launch_bounds__(256) hy_rope_append_kernel(LinOut P, int off_q
 // ([T][H][G * dv]); mixing the weights, w'_h = sum_g talk[h, g] w_g, and applying them to the values of head h's own key
 // head c(h) is the same as  out_h = sum_g talk[h, g] o[g][c(h)]  (both are linear in the weights).  Else o is [T][H][dv].
 // off_gate >= 0: head h is multiplied by sigmoid(P[t, off_gate + h]).  grid (T, ceil(H * dv / 256)).
-template <typename AT>
-__global__ void __launch_bounds__(256) hy_heads_mix_kernel(const float* __restrict__ o, const float* __restrict__ talk, LinOut P, int off_gate,
+template <typename AT, typename OT>
+__global__ void __launch_bounds__(256) hy_heads_mix_kernel(const OT* __restrict__ o, const float* __restrict__ talk, LinOut P, int off_gate,
                                                            int H, int G, int dv, AT* __restrict__ out, long long ld_out) {
   pdl_launch_dependents();
   pdl_wait();
@@ -1130,11 +1133,11 @@ __global__ void __launch_bounds__(256) hy_heads_mix_kernel(const float* __restri
   float v;
   if (talk != nullptr) {
     const int c = h / (H / G);
-    const float* ot = o + t * ((long long)H * G * dv) + (long long)c * dv + d;
+    const OT* ot = o + t * ((long long)H * G * dv) + (long long)c * dv + d;
     v = 0.f;
-    for (int g = 0; g < H; ++g) v = fmaf(talk[h * H + g], ot[(long long)g * G * dv], v);
+    for (int g = 0; g < H; ++g) v = fmaf(talk[h * H + g], act_load<OT>(ot + (long long)g * G * dv), v);
   } else {
-    v = o[t * ((long long)H * dv) + i];
+    v = act_load<OT>(o + t * ((long long)H * dv) + i);
   }
   if (off_gate >= 0) v *= hy_sigmoid(lin_at(P, t, off_gate + h));
   act_store<AT>(out + t * ld_out + i, v);

@@ -50,7 +50,7 @@ __device__ __forceinline__ uint32_t att_tile_off(int r, int c16) {
 template <int HD, int NKB>
 __device__ __forceinline__ void att_warp_block(const uint32_t (*qf)[4], uint32_t sK, uint32_t sV, int krow0, int key_abs0,
                                                int lim0, int lim1, float scale_log2, float (&mrow)[2],
-                                               float (&lrow)[2], float (*o)[4], float softcap = 0.f) {
+                                               float (&lrow)[2], float (*o)[4], float softcap = 0.f, bool p_split = false) {
   constexpr int KS = HD / 16;   // k-steps over the head dim
   constexpr int DT = HD / 8;    // output n-tiles over the head dim
   constexpr int NT = NKB * 2;   // score n-tiles (8 keys each)
@@ -102,15 +102,22 @@ __device__ __forceinline__ void att_warp_block(const uint32_t (*qf)[4], uint32_t
   mrow[0] = mn0;
   mrow[1] = mn1;
   float sum0 = 0.f, sum1 = 0.f;
-  uint32_t pa[NKB][4];
+  // p_split: the weights meet the values as two bf16 operands, p = hi + lo (16 mantissa bits instead of 8)
+  uint32_t pa[NKB][4], pb[NKB][4];
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
     const float p0 = exp2f(s[j][0] - ref0), p1 = exp2f(s[j][1] - ref0);
     const float p2 = exp2f(s[j][2] - ref1), p3 = exp2f(s[j][3] - ref1);
     sum0 += p0 + p1;
     sum1 += p2 + p3;
-    pa[j >> 1][(j & 1) * 2] = f2_to_bf2(p0, p1);
-    pa[j >> 1][(j & 1) * 2 + 1] = f2_to_bf2(p2, p3);
+    const uint32_t h01 = f2_to_bf2(p0, p1), h23 = f2_to_bf2(p2, p3);
+    pa[j >> 1][(j & 1) * 2] = h01;
+    pa[j >> 1][(j & 1) * 2 + 1] = h23;
+    if (p_split) {
+      const float2 r01 = bf2_to_f2(h01), r23 = bf2_to_f2(h23);
+      pb[j >> 1][(j & 1) * 2] = f2_to_bf2(p0 - r01.x, p1 - r01.y);
+      pb[j >> 1][(j & 1) * 2 + 1] = f2_to_bf2(p2 - r23.x, p3 - r23.y);
+    }
   }
   lrow[0] = lrow[0] * c0 + sum0;
   lrow[1] = lrow[1] * c1 + sum1;
@@ -129,6 +136,10 @@ __device__ __forceinline__ void att_warp_block(const uint32_t (*qf)[4], uint32_t
       ldsm_x4_t(sV + att_tile_off(krow, d + (mi >> 1)), b0, b1, b2, b3);
       mma_bf16_16816(o[d], pa[kb], b0, b1);
       mma_bf16_16816(o[d + 1], pa[kb], b2, b3);
+      if (p_split) {
+        mma_bf16_16816(o[d], pb[kb], b0, b1);
+        mma_bf16_16816(o[d + 1], pb[kb], b2, b3);
+      }
     }
   }
 }
@@ -185,6 +196,7 @@ struct AttDecOpt {
   float softcap;
   int v_wide;
   long long out_head_stride;
+  int p_split;   // 1: the softmax weights enter the value product as hi + lo bf16 pairs (fp32-grade weights)
 };
 struct QkvFin {
   const float* part;
@@ -338,7 +350,7 @@ __global__ void __launch_bounds__(160) xb_attn_decode_mma_kernel(
       }
       if (key_abs0 + warp * 16 <= pos) {
         const uint32_t sK = smem_u32(stages + stage * Cfg::STAGE_BYTES);
-        att_warp_block<HD, 1>(qf, sK, sK + Cfg::TILE_BYTES, warp * 16, key_abs0, pos, pos, scale_log2, mrow, lrow, o, opt.softcap);
+        att_warp_block<HD, 1>(qf, sK, sK + Cfg::TILE_BYTES, warp * 16, key_abs0, pos, pos, scale_log2, mrow, lrow, o, opt.softcap, opt.p_split != 0);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[stage]);
@@ -575,6 +587,7 @@ struct AttIo {
   float softcap;
   int v_wide;
   long long out_head_stride;
+  int p_split;   // 1: the softmax weights enter the value product as hi + lo bf16 pairs (fp32-grade weights): twice the PV MMAs
 };
 
 template <int HD, int G>
@@ -746,6 +759,9 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
           // P(kt) sits in the first 32 columns of S buffer kt&1 (16 keys = 8 packed columns per step)
           tc_mma_bf16_ts(tm_O, tm_S + (uint32_t)((kt & 1) * XB_ATT_TILE) + ks * 8, umma_desc_mn_sw128(b, XB_ATT_TILE * 128), idesc_o,
                          (kt > 0 || ks > 0) ? 1u : 0u);
+          // the low halves of the weights sit in columns 32..63 of the same S buffer
+          if (io.p_split)
+            tc_mma_bf16_ts(tm_O, tm_S + (uint32_t)((kt & 1) * XB_ATT_TILE) + 32 + ks * 8, umma_desc_mn_sw128(b, XB_ATT_TILE * 128), idesc_o, 1u);
 #else
           const uint32_t a = p_addr + ks * 32;
           tc_mma_bf16(tm_O, umma_desc_sw128(a), umma_desc_mn_sw128(b, XB_ATT_TILE * 128), idesc_o, (kt > 0 || ks > 0) ? 1u : 0u);
@@ -862,7 +878,7 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
       const float nmref = (m_used == -INFINITY) ? 0.f : -m_used;
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #if XB_ATT_P_TMEM
-      uint32_t pw[XB_ATT_TILE / 2];
+      uint32_t pw[XB_ATT_TILE / 2], pl[XB_ATT_TILE / 2];
 #endif
 #pragma unroll
       for (int c = 0; c < XB_ATT_TILE; c += 8) {
@@ -880,6 +896,17 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
 #if XB_ATT_P_TMEM
         pw[(c >> 1)] = f2_to_bf2(p[0], p[1]); pw[(c >> 1) + 1] = f2_to_bf2(p[2], p[3]);
         pw[(c >> 1) + 2] = f2_to_bf2(p[4], p[5]); pw[(c >> 1) + 3] = f2_to_bf2(p[6], p[7]);
+        if (io.p_split) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 hi = bf2_to_f2(pw[(c >> 1) + j]);
+            pl[(c >> 1) + j] = f2_to_bf2(p[2 * j] - hi.x, p[2 * j + 1] - hi.y);
+          }
+        }
+      }
+      if (io.p_split) {
+        tmem_st16(tm_Sk + lane_base + 32, pl);
+        tmem_st16(tm_Sk + lane_base + 48, pl + 16);
       }
       // P -> tensor memory, over the first 32 columns of this tile's S buffer (this row's scores are
       // already in registers; the MMA warp reads them as the A operand of O += P V)

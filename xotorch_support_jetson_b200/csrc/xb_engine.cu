@@ -828,7 +828,7 @@ static int launch_attn_decode(xb_engine* e, const LayerW& w, const BatchMeta& m,
   }
   dim3 grid(T, d.n_kv_heads, n_splits);
   XB_TRY(launch_kc(e, kern, grid, dim3(160), Cfg::SMEM_BYTES, st, dim3(1, 1, cl ? n_splits : 1), w.tmK, w.tmV, e->q, m, e->o_part,
-                   e->ml_part, e->attn, d.n_heads, d.n_kv_heads, n_splits, scale_log2, fin, cl, AttDecOpt{nullptr, 0.f, 0, 0}));
+                   e->ml_part, e->attn, d.n_heads, d.n_kv_heads, n_splits, scale_log2, fin, cl, AttDecOpt{nullptr, 0.f, 0, 0, 0}));
   if (n_splits > 1 && !cl) {
     const int rows = T * d.n_heads;
     XB_TRY(launch_k(e, xb_attn_combine2_kernel<HD>, dim3((rows + 3) / 4), dim3(128), 0, st, 1, e->o_part, e->ml_part, e->attn, n_splits, rows));

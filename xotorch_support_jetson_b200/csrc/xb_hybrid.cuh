@@ -80,6 +80,7 @@ struct HyModel {
   size_t maxQA = 0, maxE = 0, maxM = 0;   // maxM: widest matrix that passes through the m1 / m2 buffers besides the stream's width
   float* vfirst = nullptr;              // values of the first blending layer for the tokens of this step [T, G * dv]
   size_t maxGV = 0;
+  int p_split = 1;                      // XB_HY_P_SPLIT=0: rotary-position attention rounds its softmax weights to bf16 (A/B)
   int dec_splits = 1;                   // key splits of this step's single-token attention (hy_kv_splits)
   bool pdl_now = false;
   int recur_lpc = 0;         // XB_HY_LPC=4|8|16 pins the lanes per state column (A/B); 0: by the step's shape
@@ -249,6 +250,7 @@ static int hy_create_softmax(xb_engine* e, int i, bool own, uint64_t& wbytes, ui
   XB_CHECK(d.block == XB_BLOCK_SANDWICH, "layer %d: rotary-position attention belongs to sandwich blocks", i);
   XB_CHECK(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0, "layer %d: bad attention sizes", i);
   XB_CHECK(rd >= 0 && rd <= dk && rd % 2 == 0, "layer %d: %lld rotating entries do not fit a head of %lld", i, rd, dk);
+  XB_CHECK(rd / 2 <= HY_MAX_ROT_PAIRS, "layer %d: %lld rotating entries (at most %d)", i, rd, 2 * HY_MAX_ROT_PAIRS);
   XB_CHECK(c.s_rot_pairs == XB_ROPE_INTERLEAVED || c.s_rot_pairs == XB_ROPE_HALF_SPLIT, "layer %d: unknown rotary pair layout %d", i, c.s_rot_pairs);
   XB_CHECK(c.s_softcap >= 0.f && c.s_scale > 0.f, "layer %d: bad score scale %g / soft cap %g", i, c.s_scale, c.s_softcap);
   l.v_all = c.s_talk != 0 && G > 1;
@@ -589,6 +591,8 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
     if (lm != nullptr) hy->use_lat_mma = atoi(lm);   // 0: off; 1: by the step's shape; 4: always the four-warp unsplit form; 2: always key shares
     const char* ta = getenv("XB_HY_TC_ATTN");
     if (ta != nullptr && ta[0] == '0') hy->use_tc_attn = 0;
+    const char* ps = getenv("XB_HY_P_SPLIT");
+    if (ps != nullptr && ps[0] == '0') hy->p_split = 0;
     const char* lp = getenv("XB_HY_LPC");
     if (lp != nullptr && (atoi(lp) == 4 || atoi(lp) == 8 || atoi(lp) == 16)) hy->recur_lpc = atoi(lp);
   }
@@ -1112,9 +1116,14 @@ static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, const void* xin
       XB_TRY(hy_launch(e, hy_glu_clamp_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, U, c.ff, c.ff_limit, a2, (long long)l.n_dn, T));
   } else {
     // router in fp32 whatever the serving type: fp32 accumulation of the products, fp32 logits
-    const int chunks = (c.n_experts + 7) / 8;
-    XB_TRY(hy_launch(e, hy_router_logits_kernel<AT>, dim3((unsigned)(((long long)T * chunks + 7) / 8)), dim3(256), 0, st,
-                     reinterpret_cast<const AT*>(xin), (long long)D, (const bf16*)l.w_router, hy->m2, T, c.n_experts, D));
+    if (T <= 64) {   // few rows: a warp per (token, expert)
+      XB_TRY(hy_launch(e, hy_router_logits_kernel<AT, 1>, dim3((unsigned)(((long long)T * c.n_experts + 7) / 8)), dim3(256), 0, st,
+                       reinterpret_cast<const AT*>(xin), (long long)D, (const bf16*)l.w_router, hy->m2, T, c.n_experts, D));
+    } else {
+      const int chunks = (c.n_experts + 7) / 8;
+      XB_TRY(hy_launch(e, hy_router_logits_kernel<AT, 8>, dim3((unsigned)(((long long)T * chunks + 7) / 8)), dim3(256), 0, st,
+                       reinterpret_cast<const AT*>(xin), (long long)D, (const bf16*)l.w_router, hy->m2, T, c.n_experts, D));
+    }
     const LinOut z = hy_plain(hy->m2, c.n_experts);
     const size_t rs = (size_t)4 * (2 * c.n_experts + (c.groups > 0 ? c.groups : 1)) * sizeof(float);
     XB_TRY(hy_launch(e, hy_route_kernel, dim3((T + 3) / 4), dim3(128), rs, st, z, c.n_experts, c.top, c.groups, c.keep_groups, c.route_scale,
@@ -1242,6 +1251,21 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
 // Rotary-position softmax attention of one layer: P = [q | k | v | head gates] of the step's rows -> a1 = what the output
 // projection reads.  Rotation, value blending and the cache append are one kernel; the attention runs a block per
 // (token, head) over the pages; mixed heads / head gates follow in a kernel of their own.
+// mixed heads / head gates behind the tensor-core attention kernels, whose output is a bf16 matrix in hy->o
+template <typename AT>
+static int hy_heads_mix_bf16(xb_engine* e, const HyLayer& l, int T, const LinOut& P, cudaStream_t st) {
+  HyModel* hy = e->hy;
+  const xb_hybrid_layer& c = l.d;
+  const int H = c.s_heads, G = l.v_all ? c.s_kv_heads : 1, dv = c.s_vdim;
+  const float* talk = c.s_talk ? (const float*)l.talk : (const float*)nullptr;
+  AT* a1 = reinterpret_cast<AT*>(hy->a1);
+  if (dv % 8 == 0)
+    return hy_launch(e, hy_heads_mix_vec_kernel<AT>, dim3(T, (H * dv / 8 + 255) / 256), dim3(256), 0, st, (const bf16*)hy->o, talk, P,
+                     c.s_gate ? l.off_g : -1, H, G, dv, a1, (long long)l.n_o);
+  return hy_launch(e, hy_heads_mix_kernel<AT, bf16>, dim3(T, (H * dv + 255) / 256), dim3(256), 0, st, (const bf16*)hy->o, talk, P,
+                   c.s_gate ? l.off_g : -1, H, G, dv, a1, (long long)l.n_o);
+}
+
 template <typename AT>
 static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, int n_tiles, const LinOut& P, const BatchMeta& m, cudaStream_t st) {
   HyModel* hy = e->hy;
@@ -1266,25 +1290,21 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, i
     // mixed heads multiply the blocks by the key heads: fewer splits keep the grid near one wave
     int ns = l.v_all ? hy->dec_splits / G : hy->dec_splits;
     ns = ns < 1 ? 1 : ns;
-    const AttDecOpt dopt{c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : 0, (long long)dvo};
+    const AttDecOpt dopt{c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : 0, (long long)dvo, hy->p_split};
     bf16* dst = post ? reinterpret_cast<bf16*>(hy->o) : reinterpret_cast<bf16*>(hy->a1);
     if (dk == 128) XB_TRY(hy_attn_dec<128>(e, l, m, T, hy->qg, dst, H, G, c.s_scale, ns, dopt, st));
     else XB_TRY(hy_attn_dec<64>(e, l, m, T, hy->qg, dst, H, G, c.s_scale, ns, dopt, st));
-    if (post)
-      XB_TRY(hy_launch(e, hy_heads_mix_kernel<AT, bf16>, dim3(T, (H * dv + 255) / 256), dim3(256), 0, st, (const bf16*)hy->o,
-                       c.s_talk ? (const float*)l.talk : (const float*)nullptr, P, c.s_gate ? l.off_g : -1, H, l.v_all ? G : 1, dv, a1, (long long)l.n_o));
+    if (post) XB_TRY(hy_heads_mix_bf16<AT>(e, l, T, P, st));
     return 0;
   }
   if (tc) {
     HyAttnIn in;
     in.tile_start = m.tile_start; in.tile_len = m.tile_len; in.n_tiles = n_tiles; in.q = hy->qg;
-    in.io = AttIo{(long long)H * dk, nullptr, nullptr, 0, c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : 0, (long long)dvo};
+    in.io = AttIo{(long long)H * dk, nullptr, nullptr, 0, c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : 0, (long long)dvo, hy->p_split};
     bf16* dst = post ? reinterpret_cast<bf16*>(hy->o) : reinterpret_cast<bf16*>(hy->a1);
     if (dk == 128) XB_TRY(hy_attn_tc_any<128>(e, l, m, in, dst, H, G, c.s_scale, l.v_all ? G : 1, st));
     else XB_TRY(hy_attn_tc_any<64>(e, l, m, in, dst, H, G, c.s_scale, l.v_all ? G : 1, st));
-    if (post)
-      XB_TRY(hy_launch(e, hy_heads_mix_kernel<AT, bf16>, dim3(T, (H * dv + 255) / 256), dim3(256), 0, st, (const bf16*)hy->o,
-                       c.s_talk ? (const float*)l.talk : (const float*)nullptr, P, c.s_gate ? l.off_g : -1, H, l.v_all ? G : 1, dv, a1, (long long)l.n_o));
+    if (post) XB_TRY(hy_heads_mix_bf16<AT>(e, l, T, P, st));
     return 0;
   }
   const int aw = 16, far = 1 << 30;   // causal over the whole sequence: the block's warps share out all earlier keys

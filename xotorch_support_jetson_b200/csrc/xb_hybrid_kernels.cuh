@@ -1048,6 +1048,7 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
 // Rotation of the first `dims` entries of a head: entry pairs (i, i + dims/2) (half = 1) or (2i, 2i + 1) (half = 0);
 // (u, v) -> (u c - v s, v c + u s) with c, s = mult * cos / sin(pos * freq[i]).  The angle is formed in double and reduced
 // to [-pi, pi] there, so that its error does not grow with the position.
+#define HY_MAX_ROT_PAIRS 256   // rotating pairs per head (key dim <= 512)
 struct RotArgs {
   const double* freq;   // [dims / 2]
   int dims, half;
@@ -1079,6 +1080,10 @@ __global__ void __launch_bounds__(256) hy_rope_append_kernel(LinOut P, int off_q
   const int in_page = pos % m.page_tokens;
   const int hp = r.dims >> 1, per = dk - hp;   // units of one query / key head
   const int n_qk = (H + G) * per, total = n_qk + G * dv;
+  // every head of the token turns by the same angles: cos / sin of the pairs once per block
+  __shared__ float cs_tab[2 * HY_MAX_ROT_PAIRS];
+  for (int j = threadIdx.x; j < hp; j += blockDim.x) hy_rot_cs(r, pos, j, &cs_tab[2 * j], &cs_tab[2 * j + 1]);
+  __syncthreads();
   for (int u = blockIdx.y * blockDim.x + threadIdx.x; u < total; u += blockDim.x * gridDim.y) {
     if (u < n_qk) {
       const int hd = u / per, j = u - hd * per;
@@ -1090,8 +1095,7 @@ __global__ void __launch_bounds__(256) hy_rope_append_kernel(LinOut P, int off_q
       if (j < hp) {
         const int d0 = r.half ? j : 2 * j, d1 = r.half ? j + hp : 2 * j + 1;
         const float a = lin_at(P, row, src + d0), b = lin_at(P, row, src + d1);
-        float c, sn;
-        hy_rot_cs(r, pos, j, &c, &sn);
+        const float c = cs_tab[2 * j], sn = cs_tab[2 * j + 1];
         const float y0 = a * c - b * sn, y1 = b * c + a * sn;
         if (!is_q) { act_store<KT>(ko + d0, y0); act_store<KT>(ko + d1, y1); }
         else if (q16 != nullptr) { q16[qi + d0] = f2bf(y0); q16[qi + d1] = f2bf(y1); }
@@ -1141,6 +1145,44 @@ __global__ void __launch_bounds__(256) hy_heads_mix_kernel(const OT* __restrict_
   }
   if (off_gate >= 0) v *= hy_sigmoid(lin_at(P, t, off_gate + h));
   act_store<AT>(out + t * ld_out + i, v);
+}
+
+__device__ __forceinline__ void hy_load8(const bf16* p, const float* bias, float* v);   // eight bf16 neighbours as floats (below)
+// The same on the bf16 matrix the tensor-core attention leaves, eight neighbouring channels per thread (dv a multiple of 8).
+// grid (T, ceil(H * dv / 8 / 256)).
+template <typename AT>
+__global__ void __launch_bounds__(256) hy_heads_mix_vec_kernel(const bf16* __restrict__ o, const float* __restrict__ talk, LinOut P, int off_gate,
+                                                               int H, int G, int dv, AT* __restrict__ out, long long ld_out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  const int i8 = blockIdx.y * blockDim.x + threadIdx.x, dv8 = dv >> 3;
+  if (i8 >= H * dv8) return;
+  const int h = i8 / dv8, d = (i8 - h * dv8) << 3;
+  float acc[8];
+  if (talk != nullptr) {
+    const int c = h / (H / G);
+    const bf16* ot = o + t * ((long long)H * G * dv) + (long long)c * dv + d;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int g = 0; g < H; ++g) {
+      float x[8];
+      hy_load8(ot + (long long)g * G * dv, nullptr, x);
+      const float w = talk[h * H + g];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(w, x[j], acc[j]);
+    }
+  } else {
+    hy_load8(o + t * ((long long)H * dv) + (long long)h * dv + d, nullptr, acc);
+  }
+  if (off_gate >= 0) {
+    const float gt = hy_sigmoid(lin_at(P, t, off_gate + h));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= gt;
+  }
+  AT* dst = out + t * ld_out + (long long)h * dv + d;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) act_store<AT>(dst + j, acc[j]);
 }
 
 // ----------------------------------------------------------------------------- feed-forward activation, side input, logits
@@ -1564,29 +1606,30 @@ __global__ void hy_moe_act_vec_kernel(const bf16* __restrict__ u, long long ld, 
 // Router logits in fp32 for any number of rows: z[t, e] = sum_k x[t, k] w[e, k].  A warp takes one token and up to eight
 // experts: it reads the token's row once and streams eight weight rows (which stay in L1 / L2 across tokens).
 // grid (ceil(T * ceil(E / 8) / 8)), 256 threads.
-template <typename AT>
+// EPW: experts per warp, 8 for prompts; 1 in steps of few rows, where T * E warps are what fills the GPU.
+template <typename AT, int EPW>
 __global__ void __launch_bounds__(256) hy_router_logits_kernel(const AT* __restrict__ x, long long ldx, const bf16* __restrict__ w,
                                                                float* __restrict__ z, int T, int E, int K) {
   pdl_launch_dependents();
   pdl_wait();
-  const int chunks = (E + 7) >> 3;
+  const int chunks = (E + EPW - 1) / EPW;
   const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (wid >= (long long)T * chunks) return;
   const long long t = wid / chunks;
-  const int e0 = (int)(wid - t * chunks) << 3;
-  const int ne = E - e0 < 8 ? E - e0 : 8;
+  const int e0 = (int)(wid - t * chunks) * EPW;
+  const int ne = E - e0 < EPW ? E - e0 : EPW;
   const AT* xr = x + t * ldx;
-  float acc[8];
+  float acc[EPW];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  for (int j = 0; j < EPW; ++j) acc[j] = 0.f;
   if ((K & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
     for (int k = lane * 8; k < K; k += 256) {
       float xv[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) xv[i] = act_load<AT>(xr + k + i);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < EPW; ++j) {
         if (j < ne) {
           const uint4 u = *reinterpret_cast<const uint4*>(w + (long long)(e0 + j) * K + k);
           const float2 a = bf2_to_f2(u.x), b = bf2_to_f2(u.y), c = bf2_to_f2(u.z), d = bf2_to_f2(u.w);
@@ -1601,12 +1644,12 @@ __global__ void __launch_bounds__(256) hy_router_logits_kernel(const AT* __restr
     for (int k = lane; k < K; k += 32) {
       const float xv = act_load<AT>(xr + k);
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
+      for (int j = 0; j < EPW; ++j)
         if (j < ne) acc[j] = fmaf(xv, bf2f(w[(long long)(e0 + j) * K + k]), acc[j]);
     }
   }
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < EPW; ++j) {
     const float v = warp_sum(acc[j]);
     if (lane == 0 && j < ne) z[t * E + e0 + j] = v;
   }

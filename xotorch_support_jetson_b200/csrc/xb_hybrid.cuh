@@ -1280,7 +1280,10 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, i
   const bool tc = std::is_same<AT, bf16>::value && l.tc_attn && hy->use_tc_attn && n_tiles > 0;
   // steps of single tokens, same sizes: the split-key decode kernel (its splits merge inside a cluster)
   const bool dec = std::is_same<AT, bf16>::value && l.tc_attn && hy->use_tc_attn && n_tiles == 0 && T == n_seqs && e->attn_cluster != 0;
-  XB_TRY(hy_launch(e, hy_rope_append_kernel<KT>, dim3(T, (units + 255) / 256), dim3(256), 0, st, P, l.off_q, l.off_k, l.off_v, H, G, dk, dv, r,
+  // prompts: a block walks all units of its token (the row's position, page and angles are fetched once); few rows: a block
+  // per 256 units so that the step fills more SMs
+  const int rope_by = T >= 512 ? 1 : (units + 255) / 256;
+  XB_TRY(hy_launch(e, hy_rope_append_kernel<KT>, dim3(T, rope_by), dim3(256), 0, st, P, l.off_q, l.off_k, l.off_v, H, G, dk, dv, r,
                    hy->qa, (tc || dec) ? hy->qg : (bf16*)nullptr, (KT*)l.k_pool, (KT*)l.v_pool, l.v_all ? 1 : 0, (const float*)l.vmix, hy->vfirst,
                    l.vmode, m));
   const int dvo = l.v_all ? G * dv : dv;

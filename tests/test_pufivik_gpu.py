@@ -113,6 +113,8 @@ ALONE = {
   "sink_attention_one_key_head": config([(sink_attn(heads=3, kv=1, dim=16, vdim=24, dims=16), None)], groups=1, taps=1),
   "sink_attention_every_head_its_own_keys": config([(sink_attn(heads=3, kv=3, dim=12, vdim=12, dims=4, scaling=None), None)], mult=1.0),
   "sink_attention_no_rotation_wide_values": config([(sink_attn(heads=4, kv=4, dim=8, vdim=120, dims=0, scaling=None), None)], taps=0),
+  "sink_attention_values_wider_than_a_block": config([(sink_attn(heads=4, kv=4, dim=8, vdim=136, dims=4), None)], width=64, groups=2),
+  "cap_attention_values_wider_than_a_block": config([(cap_attn(heads=2, kv=1, dim=8, vdim=600, dims=4), None)], width=64, groups=2),
   "sink_attention_bands_all_three": config([(sink_attn(dim=32, dims=32, base=10000.0, scaling=bands(4.0, 1.0, 8.0, 256)), None)]),
   "cap_attention": config([(cap_attn(), None)]),
   "cap_attention_odd_sizes": config([(cap_attn(heads=5, kv=1, dim=10, vdim=6, dims=10, base=7.0), None)], width=50, vocab=77, groups=2, taps=5),

@@ -255,7 +255,6 @@ static int hy_create_softmax(xb_engine* e, int i, bool own, uint64_t& wbytes, ui
   XB_CHECK(c.s_softcap >= 0.f && c.s_scale > 0.f, "layer %d: bad score scale %g / soft cap %g", i, c.s_scale, c.s_softcap);
   l.v_all = c.s_talk != 0 && G > 1;
   const long long dvo = l.v_all ? G * dv : dv;   // value channels one (token, head) block of the attention kernel carries
-  XB_CHECK(dvo <= 512, "layer %d: %lld value channels per query head (mixed heads read every key head's values; at most 512)", i, dvo);
   l.off_q = 0; l.off_k = (int)(H * dk); l.off_v = l.off_k + (int)(G * dk); l.off_g = l.off_v + (int)(G * dv);
   l.n_in = l.off_g + (c.s_gate ? (int)H : 0);
   l.n_o = (int)(H * dv);
@@ -1195,10 +1194,10 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
       const int far = 1 << 30;
       if (R <= 256)
         XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 8>, dim3(T, H), dim3(32 * aw), asm_bytes, st, Q, 0, -1, (const KT*)l.k_pool,
-                         (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R, AttnOpt{nullptr, 0.f, 1}));
+                         (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R, AttnOpt{nullptr, 0.f, 1, 0}));
       else
         XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 16>, dim3(T, H), dim3(32 * aw), asm_bytes, st, Q, 0, -1, (const KT*)l.k_pool,
-                         (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R, AttnOpt{nullptr, 0.f, 1}));
+                         (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R, AttnOpt{nullptr, 0.f, 1, 0}));
       }
     latent_done:
       XB_TRY(hy_launch(e, hy_head_mm_kernel<AT>, dim3((T + HY_MM_ROWS - 1) / HY_MM_ROWS, H), dim3(128), mm2, st, (const float*)hy->o,
@@ -1287,7 +1286,8 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, i
                    hy->qa, (tc || dec) ? hy->qg : (bf16*)nullptr, (KT*)l.k_pool, (KT*)l.v_pool, l.v_all ? 1 : 0, (const float*)l.vmix, hy->vfirst,
                    l.vmode, m));
   const int dvo = l.v_all ? G * dv : dv;
-  const AttnOpt opt{c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : G};
+  const int vch = dvo > 512 ? 512 : 0;   // wider value rows: blocks along z take 512 channels each
+  const AttnOpt opt{c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : G, vch};
   const bool post = c.s_talk != 0 || c.s_gate != 0;
   if (dec) {
     // mixed heads multiply the blocks by the key heads: fewer splits keep the grid near one wave
@@ -1311,11 +1311,11 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, i
     return 0;
   }
   const int aw = 16, far = 1 << 30;   // causal over the whole sequence: the block's warps share out all earlier keys
-  const size_t asm_bytes = (size_t)(((dk + 3) & ~3) + aw * (2 + dvo)) * sizeof(float);
+  const size_t asm_bytes = (size_t)(((dk + 3) & ~3) + aw * (2 + (vch ? vch : dvo))) * sizeof(float);
   const LinOut Q = hy_plain(hy->qa, (long long)H * dk);
   const KT* kp = (const KT*)l.k_pool;
   const KT* vp = (const KT*)l.v_pool;
-  const dim3 grid(T, H), block(32 * aw);
+  const dim3 grid(T, H, vch ? (dvo + vch - 1) / vch : 1), block(32 * aw);
   if (post) {
     if (dvo <= 256)
       XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 8>, grid, block, asm_bytes, st, Q, 0, -1, kp, vp, m, H, G, dk, dvo, dk, dvo, far, 0,
@@ -1420,7 +1420,7 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
         const size_t asm_bytes = (size_t)(((dk + 3) & ~3) + aw * (2 + dv)) * sizeof(float);
         XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, AT, 8>, dim3(T, H), dim3(32 * aw), asm_bytes, st, P, l.off_q, l.off_g,
                          (const KT*)l.k_pool, (const KT*)l.v_pool, m, H, G, dk, dv, dk, dv, c.a_window, c.a_keep_first, c.a_scale, 1.0f, a1,
-                         (long long)l.n_o, AttnOpt{nullptr, 0.f, G}));
+                         (long long)l.n_o, AttnOpt{nullptr, 0.f, G, 0}));
       }
       const long long ldc = 2LL * Hr * rk + (long long)Hr * rv;
       XB_TRY(hy_launch(e, hy_hgrn_prep_kernel, dim3(T, (2 * Hr * rk + Hr * rv + 255) / 256), dim3(256), 0, st, P, l.off_rq, l.off_rf, l.off_rv, (const float*)l.lower, hy->c,

@@ -904,10 +904,13 @@ __global__ void hy_qg_pack_kernel(LinOut P, int off_q, int nq, int off_g, int ng
 // denominator, with no key and no value.  softcap > 0: score <- cap * tanh(score / cap) (after the scale).  v_heads: value
 // heads per page of the value pool; 1 while G > 1 means a value row holds every key head's values side by side
 // ([page][token][G * dv], dv here = that whole width), so that one query head's weights meet all of them.
+// v_chunk > 0: block z handles value channels [z * v_chunk, (z + 1) * v_chunk) of the row (rows wider than the 512 channels a
+// block's lanes can carry; every block recomputes the scores).
 struct AttnOpt {
   const float* sink;
   float softcap;
   int v_heads;
+  int v_chunk;
 };
 template <typename KT, typename AT, int NACC>
 __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q, int off_gate, const KT* __restrict__ k_pool,
@@ -919,6 +922,13 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
   extern __shared__ __align__(16) float qsm[];
   const int row = blockIdx.x, h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int dv_full = dv;
+  int voff = 0;
+  if (opt.v_chunk > 0) {
+    voff = (int)blockIdx.z * opt.v_chunk;
+    dv = dv_full - voff < opt.v_chunk ? dv_full - voff : opt.v_chunk;
+    v_pool += voff;
+  }
   float* q = qsm;
   float* part = qsm + ((dk + 3) & ~3);   // per warp: max, sum, acc[dv]
   for (int i = threadIdx.x; i < dk; i += blockDim.x) q[i] = lin_at(P, row, off_q + h * dk + i) * scale;
@@ -1038,8 +1048,8 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
     const int d = lane + 32 * c;
     if (d < dv) {
       float v = acc[c] * inv;
-      if (off_gate >= 0) v *= hy_sigmoid(lin_at(P, row, off_gate + h * dv + d));
-      act_store<AT>(out + (long long)row * ld_out + (long long)h * dv + d, v);
+      if (off_gate >= 0) v *= hy_sigmoid(lin_at(P, row, off_gate + h * dv_full + voff + d));
+      act_store<AT>(out + (long long)row * ld_out + (long long)h * dv_full + voff + d, v);
     }
   }
 }

@@ -803,7 +803,8 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
     }
     float m_used = -INFINITY;     // reference max (scaled, log2 units) that O and l are expressed against
     float l_sum = 0.f;
-    const float sl2 = io.softcap > 0.f ? 1.4426950408889634f : scale_log2;       // what turns a score in v[] into log2 units
+    const float sl2 = io.softcap > 0.f ? 1.0f : scale_log2;                       // what turns a score in v[] into log2 units
+    const float cl2 = io.softcap * 1.4426950408889634f;
     const float cap_k = io.softcap > 0.f ? 2.0f * scale_log2 / io.softcap : 0.f;  // raw product -> 2 s / cap in log2 units
     for (int kt = 0; kt < n_kt; ++kt) {
       mbar_wait(&s_full[kt & 1], (kt >> 1) & 1);
@@ -816,13 +817,14 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
       for (int c = 0; c < XB_ATT_TILE; c += 16) tmem_ld16(tm_Sk + lane_base + c, v + c);
       tmem_ld_wait();
       if (io.softcap > 0.f) {
-        // capped score cap * tanh(s / cap) in place of the raw product, tanh(x) = 1 - 2 / (1 + e^(2x)); the softmax below
-        // then works on natural-log scores (sl2 = log2 e)
+        // capped score cap * tanh(s / cap) in place of the raw product, tanh(x) = 1 - 2 / (1 + e^(2x)), already in log2
+        // units (cl2 = cap * log2 e), so the softmax below takes it as it is (sl2 = 1): five instructions per score
 #pragma unroll
         for (int j = 0; j < XB_ATT_TILE; ++j) {
-          float ex;
+          float ex, rc;
           asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(__uint_as_float(v[j]) * cap_k));
-          v[j] = __float_as_uint(io.softcap * (1.0f - __fdividef(2.0f, 1.0f + ex)));
+          asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(1.0f + ex));
+          v[j] = __float_as_uint(fmaf(-2.0f * cl2, rc, cl2));
         }
       }
       // only tiles that reach past the first row's position, or (with a window) back beyond the last row's window,

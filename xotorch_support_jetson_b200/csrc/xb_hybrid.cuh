@@ -1282,6 +1282,12 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, i
   // prompts: a block walks all units of its token (the row's position, page and angles are fetched once); few rows: a block
   // per 256 units so that the step fills more SMs
   const int rope_by = T >= 512 ? 1 : (units + 255) / 256;
+  const bool rope_vec = tc && P.h != nullptr && P.bias == nullptr && P.ld % 8 == 0 && dk % 8 == 0 && dv % 8 == 0 &&
+                        c.s_rot_dims % (r.half ? 16 : 8) == 0 && (G * dv) % 8 == 0;
+  if (rope_vec)   // a prompt whose projection came back as a bf16 matrix: 16 bytes per thread
+    XB_TRY(hy_launch(e, hy_rope_append_vec_kernel, dim3(T), dim3(256), 0, st, P.h, P.ld, l.off_q, l.off_k, l.off_v, H, G, dk, dv, r, hy->qg,
+                     (bf16*)l.k_pool, (bf16*)l.v_pool, l.v_all ? 1 : 0, (const float*)l.vmix, hy->vfirst, l.vmode, m));
+  else
   XB_TRY(hy_launch(e, hy_rope_append_kernel<KT>, dim3(T, rope_by), dim3(256), 0, st, P, l.off_q, l.off_k, l.off_v, H, G, dk, dv, r,
                    hy->qa, (tc || dec) ? hy->qg : (bf16*)nullptr, (KT*)l.k_pool, (KT*)l.v_pool, l.v_all ? 1 : 0, (const float*)l.vmix, hy->vfirst,
                    l.vmode, m));

@@ -1130,6 +1130,86 @@ __global__ void __launch_bounds__(256) hy_rope_append_kernel(LinOut P, int off_q
   }
 }
 
+// The same for prompts in bf16 serving, eight neighbouring entries per thread (16-byte loads and stores): P is the bf16 matrix
+// the tensor-core Linear left (no bias), queries leave as bf16 rows for the tensor-core attention.  Wants dk, dv, the row pitch
+// and the column offsets to be multiples of 8, and the rotating part a multiple of 8 entries (pairs (2i, 2i+1)) or of 16
+// (pairs (i, i + dims/2): a thread turns the 8 entries at d together with the 8 at d + dims/2).  grid (T), 256 threads.
+__device__ __forceinline__ void hy_load8(const bf16* p, const float* bias, float* v);   // eight bf16 neighbours as floats (below)
+__device__ __forceinline__ uint4 hy_pack8(const float* y) {
+  return make_uint4(f2_to_bf2(y[0], y[1]), f2_to_bf2(y[2], y[3]), f2_to_bf2(y[4], y[5]), f2_to_bf2(y[6], y[7]));
+}
+__global__ void __launch_bounds__(256) hy_rope_append_vec_kernel(const bf16* __restrict__ P, long long ldp, int off_q, int off_k, int off_v, int H,
+                                                                 int G, int dk, int dv, RotArgs r, bf16* __restrict__ q16,
+                                                                 bf16* __restrict__ k_pool, bf16* __restrict__ v_pool, int v_all,
+                                                                 const float* __restrict__ vmix, float* __restrict__ vfirst, int vmode,
+                                                                 BatchMeta m) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const int s = m.tok_seq[row], pos = m.tok_pos[row];
+  const long long page = m.page_table[(long long)m.seq_slot[s] * m.max_pages + pos / m.page_tokens];
+  const int in_page = pos % m.page_tokens;
+  const int hp = r.dims >> 1, dk8 = dk >> 3;
+  __shared__ float cs_tab[2 * HY_MAX_ROT_PAIRS];
+  for (int j = threadIdx.x; j < hp; j += blockDim.x) hy_rot_cs(r, pos, j, &cs_tab[2 * j], &cs_tab[2 * j + 1]);
+  __syncthreads();
+  const bf16* prow = P + (long long)row * ldp;
+  const int n_qk = (H + G) * dk8, total = n_qk + ((G * dv) >> 3);
+  for (int u = threadIdx.x; u < total; u += blockDim.x) {
+    if (u < n_qk) {
+      const int hd = u / dk8, d = (u - hd * dk8) << 3;
+      const bool is_q = hd < H;
+      const int h = is_q ? hd : hd - H;
+      const bf16* src = prow + (is_q ? off_q : off_k) + h * dk;
+      bf16* dst = is_q ? q16 + (long long)row * H * dk + (long long)h * dk : k_pool + ((page * G + h) * m.page_tokens + in_page) * dk;
+      float a[8], y0[8];
+      if (d >= r.dims) {                       // entries that do not turn
+        *reinterpret_cast<uint4*>(dst + d) = *reinterpret_cast<const uint4*>(src + d);
+      } else if (!r.half) {                    // pairs (2i, 2i + 1): four of them in this chunk
+        hy_load8(src + d, nullptr, a);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float c = cs_tab[2 * ((d >> 1) + i)], sn = cs_tab[2 * ((d >> 1) + i) + 1];
+          y0[2 * i] = a[2 * i] * c - a[2 * i + 1] * sn;
+          y0[2 * i + 1] = a[2 * i + 1] * c + a[2 * i] * sn;
+        }
+        *reinterpret_cast<uint4*>(dst + d) = hy_pack8(y0);
+      } else if (d < hp) {                     // pairs (i, i + dims/2): this chunk and its partner
+        float b[8], y1[8];
+        hy_load8(src + d, nullptr, a);
+        hy_load8(src + d + hp, nullptr, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float c = cs_tab[2 * (d + i)], sn = cs_tab[2 * (d + i) + 1];
+          y0[i] = a[i] * c - b[i] * sn;
+          y1[i] = b[i] * c + a[i] * sn;
+        }
+        *reinterpret_cast<uint4*>(dst + d) = hy_pack8(y0);
+        *reinterpret_cast<uint4*>(dst + d + hp) = hy_pack8(y1);
+      }                                        // chunks in [dims/2, dims) were written by their partners
+    } else {
+      const int i = (u - n_qk) << 3;
+      float v[8];
+      hy_load8(prow + off_v + i, nullptr, v);
+      float* vf = vfirst + (long long)row * G * dv + i;
+      if (vmode == 1) {
+        *reinterpret_cast<float4*>(vf) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(vf + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      } else if (vmode == 2) {
+        const float lam = vmix[0];
+        const float4 f0 = *reinterpret_cast<const float4*>(vf), f1 = *reinterpret_cast<const float4*>(vf + 4);
+        const float fv[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (1.0f - lam) * v[j] + lam * fv[j];
+      }
+      const int g = i / dv, d = i - g * dv;
+      bf16* vo = v_all ? v_pool + (page * m.page_tokens + in_page) * ((long long)G * dv) + i
+                       : v_pool + ((page * G + g) * m.page_tokens + in_page) * dv + d;
+      *reinterpret_cast<uint4*>(vo) = hy_pack8(v);
+    }
+  }
+}
+
 // What follows the attention of an XB_MIX_SOFTMAX layer with mixed heads and / or head gates.
 // talk != nullptr: o holds, per token and query head g, that head's softmax weights applied to the values of EVERY key head
 // ([T][H][G * dv]); mixing the weights, w'_h = sum_g talk[h, g] w_g, and applying them to the values of head h's own key
@@ -1157,7 +1237,6 @@ __global__ void __launch_bounds__(256) hy_heads_mix_kernel(const OT* __restrict_
   act_store<AT>(out + t * ld_out + i, v);
 }
 
-__device__ __forceinline__ void hy_load8(const bf16* p, const float* bias, float* v);   // eight bf16 neighbours as floats (below)
 // The same on the bf16 matrix the tensor-core attention leaves, eight neighbouring channels per thread (dv a multiple of 8).
 // grid (T, ceil(H * dv / 8 / 256)).
 template <typename AT>

@@ -235,7 +235,7 @@ def test_first_tokens_and_single_token_prompt(mixed):
 
 def test_long_decoding(mixed):
   """350 decoded tokens behind a 300-token prompt: every step reads all earlier positions across many 8-token pages and
-  more than one 512-key round of the attention block; rotations reach positions near 650."""
+  more than one 512-key pass of the attention block; rotations reach positions near 650."""
   cfg, w, st = mixed
   ids = toks(650, cfg["vocab"], 31)
   ref = logits(cfg, w, ids)
@@ -299,7 +299,7 @@ def test_far_key_at_page_and_tile_borders_and_first_positions(lib, kind):
 
 @pytest.mark.parametrize("kind", ["attention", "attention_2"])
 def test_far_key_among_hundreds(lib, kind):
-  """The planted key lies 500 to 600 positions back, at the borders of the block's 512-key rounds."""
+  """The planted key lies 500 to 600 positions back, at the borders of the block's 512-key passes."""
   cfg, w = planted(kind)
   st = stage(cfg, w, "float32", page=8)
   for at in (3, 88, 89):

@@ -379,6 +379,42 @@ def test_filter_tail_across_portions_of_two_tokens(lib):
   assert rel(torch.cat(out), ref) < TOL["float32"]
 
 
+def test_experts_gathered_in_steps_of_few_rows(lib, monkeypatch):
+  """Steps whose rows cannot reach half of the experts read the chosen experts only; steps of more rows run all experts as one
+  wide product.  One, two and three sequences decoded side by side (the third step shape takes the wide form): float32 against
+  the oracle; bf16 against the engine with the gathered form switched off (same router, so the same experts are chosen)."""
+  cfg = config([(cap_attn(), experts(n=16, top=3, ff=24)), (sink_attn(), experts(n=12, top=1, ff=40))], width=64, groups=2)
+  w = weights(cfg, seed=27)
+  seqs = [toks(24, cfg["vocab"], 50 + i) for i in range(3)]
+  refs = [logits(cfg, w, s) for s in seqs]
+
+  def decode(st, n):
+    outs = [[] for _ in range(n)]
+    for p in range(24):
+      t = torch.tensor([seqs[i][p] for i in range(n)], dtype=torch.int32, device="cuda")
+      o = st.forward(list(range(n)), [1] * n, [p] * n, tokens=t, want_rows=list(range(n))).cpu().double()
+      for i in range(n):
+        outs[i].append(o[i:i + 1])
+    for i in range(n):
+      st.release_slot(i)
+    return [torch.cat(o) for o in outs]
+
+  st = stage(cfg, w, "float32")
+  for n in (1, 2, 3):
+    for i, got in enumerate(decode(st, n)):
+      assert rel(got, refs[i]) < TOL["float32"], (n, i)
+  st.close()
+  monkeypatch.setenv("XB_HY_GATHER", "0")
+  wide = stage(cfg, w, "bfloat16")
+  monkeypatch.delenv("XB_HY_GATHER")
+  st = stage(cfg, w, "bfloat16")
+  for n in (1, 2):
+    for i, (got, ref) in enumerate(zip(decode(st, n), decode(wide, n))):
+      assert rel(got, ref) < TOL["bfloat16"] / 2, (n, i)
+  st.close()
+  wide.close()
+
+
 # ----------------------------------------------------------------------------- bf16 serving
 def test_bf16_prompt_equals_token_by_token(lib):
   """bf16 serving at sizes the tensor-core Linears take: a 300-token prompt (bf16 matrices out of the Linears) against the

@@ -80,6 +80,7 @@ struct HyModel {
   size_t maxQA = 0, maxE = 0, maxM = 0;   // maxM: widest matrix that passes through the m1 / m2 buffers besides the stream's width
   float* vfirst = nullptr;              // values of the first blending layer for the tokens of this step [T, G * dv]
   size_t maxGV = 0;
+  int use_gather = 1;                   // XB_HY_GATHER=0: experts always as one wide Linear pair (A/B)
   int p_split = 1;                      // XB_HY_P_SPLIT=0: rotary-position attention rounds its softmax weights to bf16 (A/B)
   int dec_splits = 1;                   // key splits of this step's single-token attention (hy_kv_splits)
   bool pdl_now = false;
@@ -590,6 +591,8 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
     if (lm != nullptr) hy->use_lat_mma = atoi(lm);   // 0: off; 1: by the step's shape; 4: always the four-warp unsplit form; 2: always key shares
     const char* ta = getenv("XB_HY_TC_ATTN");
     if (ta != nullptr && ta[0] == '0') hy->use_tc_attn = 0;
+    const char* ga = getenv("XB_HY_GATHER");
+    if (ga != nullptr && ga[0] == '0') hy->use_gather = 0;
     const char* ps = getenv("XB_HY_P_SPLIT");
     if (ps != nullptr && ps[0] == '0') hy->p_split = 0;
     const char* lp = getenv("XB_HY_LPC");
@@ -1102,6 +1105,23 @@ static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, const void* xin
   const xb_hybrid_layer& c = l.d;
   const int D = hy->d.dim;
   AT* a2 = reinterpret_cast<AT*>(hy->a2);
+  // Steps of so few rows that at most half of the experts can have a token: read the chosen experts' rows only (two kernels
+  // in place of the wide up Linear, the activation and the wide down Linear).
+  if (c.ff_kind == XB_FF_MOE && hy->use_gather && c.shared_ff <= 0 && l.b_up == nullptr && l.b_down == nullptr && D % 8 == 0 && c.ff % 8 == 0 &&
+      2LL * T * c.top <= c.n_experts) {
+    XB_TRY(hy_launch(e, hy_router_logits_kernel<AT, 1>, dim3((unsigned)(((long long)T * c.n_experts + 7) / 8)), dim3(256), 0, st,
+                     reinterpret_cast<const AT*>(xin), (long long)D, (const bf16*)l.w_router, hy->m2, T, c.n_experts, D));
+    const size_t rs = (size_t)4 * (2 * c.n_experts + (c.groups > 0 ? c.groups : 1)) * sizeof(float);
+    XB_TRY(hy_launch(e, hy_route_kernel, dim3((T + 3) / 4), dim3(128), rs, st, hy_plain(hy->m2, c.n_experts), c.n_experts, c.top, c.groups,
+                     c.keep_groups, c.route_scale, hy->gw, T));
+    const long long nu = (long long)T * c.top * c.ff, nd = (long long)T * D;
+    XB_TRY(hy_launch(e, hy_moe_gather_up_kernel<AT>, dim3((unsigned)((nu + 7) / 8)), dim3(256), 0, st, reinterpret_cast<const AT*>(xin), (long long)D,
+                     (const bf16*)l.w_up, (const float*)hy->gw, c.n_experts, c.top, c.ff, D, c.ff_limit, c.ff_act, c.route_input, a2, T));
+    XB_TRY(hy_launch(e, hy_moe_gather_down_kernel<AT>, dim3((unsigned)((nd + 7) / 8)), dim3(256), 0, st, (const AT*)a2, (const bf16*)l.w_down,
+                     (const float*)hy->gw, c.n_experts, c.top, c.ff, D, hy->m2, T));   // m2: the router's logits there are spent
+    *y = hy_plain(hy->m2, D);
+    return 0;
+  }
   LinOut U;
   XB_TRY(hy_linear<AT>(e, xin, D, l.w_up, l.t_up, l.b_up, T, l.n_up, D, hy->P, hy->cap_P, st, &U));
   // a bf16 matrix out of the tcgen05 Linear (prompts): the activations read and write 16 bytes per thread

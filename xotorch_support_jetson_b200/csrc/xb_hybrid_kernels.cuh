@@ -1828,6 +1828,81 @@ __global__ void hy_moe_act_kernel(LinOut U, const float* __restrict__ gw, int E,
   act_store<AT>(out + t * ld_out + i, v);
 }
 
+// Experts gathered: steps of so few rows that most experts have no token read only the rows of the chosen experts instead of
+// running every expert as one wide Linear.  gw [T, E] holds the routing weights (zero = not chosen; exactly `top` are not).
+// Up: a warp per (token, chosen expert j, channel r) forms the gate and the up product of that channel (16-byte weight loads,
+// fp32 sums) and applies hy_expert_act; out[t, j * F + r].  Wants D and F multiples of 8.  grid ceil(T * top * F / 8), 256 threads.
+__device__ __forceinline__ int hy_nth_chosen(const float* __restrict__ gwt, int E, int j) {
+  int seen = 0;
+  for (int e = 0; e < E; ++e)
+    if (gwt[e] != 0.f && seen++ == j) return e;
+  return -1;
+}
+template <typename AT>
+__global__ void __launch_bounds__(256) hy_moe_gather_up_kernel(const AT* __restrict__ x, long long ldx, const bf16* __restrict__ w_up,
+                                                               const float* __restrict__ gw, int E, int top, int F, int D, float limit,
+                                                               int act, int on_input, AT* __restrict__ out, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)T * top * F) return;
+  const int t = (int)(wid / ((long long)top * F));
+  const int rem = (int)(wid - (long long)t * top * F);
+  const int j = rem / F, r = rem - j * F;
+  const int e = hy_nth_chosen(gw + (long long)t * E, E, j);
+  float v = 0.f;
+  if (e >= 0) {
+    const bf16* wg = w_up + ((long long)2 * e * F + r) * D;
+    const bf16* wu = wg + (long long)F * D;
+    const AT* xr = x + (long long)t * ldx;
+    float g = 0.f, u = 0.f;
+    for (int k = lane * 8; k < D; k += 256) {
+      float xv[8], a[8], b[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) xv[i] = act_load<AT>(xr + k + i);
+      hy_load8(wg + k, nullptr, a);
+      hy_load8(wu + k, nullptr, b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { g = fmaf(xv[i], a[i], g); u = fmaf(xv[i], b[i], u); }
+    }
+    g = warp_sum(g);
+    u = warp_sum(u);
+    v = hy_expert_act(g, u, gw[(long long)t * E + e], limit, act, on_input);
+  }
+  if (lane == 0) act_store<AT>(out + (long long)t * top * F + rem, v);
+}
+// Down: a warp per (token, output channel d) sums over the chosen experts' column blocks of the one down matrix [D, E * F].
+// y [T, D] fp32.  grid ceil(T * D / 8), 256 threads.
+template <typename AT>
+__global__ void __launch_bounds__(256) hy_moe_gather_down_kernel(const AT* __restrict__ a, const bf16* __restrict__ w_down,
+                                                                 const float* __restrict__ gw, int E, int top, int F, int D,
+                                                                 float* __restrict__ y, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)T * D) return;
+  const int t = (int)(wid / D), d = (int)(wid - (long long)t * D);
+  const float* gwt = gw + (long long)t * E;
+  const bf16* wrow = w_down + (long long)d * E * F;
+  float acc = 0.f;
+  int j = 0;
+  for (int e = 0; e < E && j < top; ++e) {
+    if (gwt[e] == 0.f) continue;
+    const AT* ar = a + (long long)t * top * F + (long long)j * F;
+    for (int k = lane * 8; k < F; k += 256) {
+      float w[8];
+      hy_load8(wrow + (long long)e * F + k, nullptr, w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc = fmaf(act_load<AT>(ar + k + i), w[i], acc);
+    }
+    ++j;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) y[(long long)t * D + d] = acc;
+}
+
 // ----------------------------------------------------------------------------- loader: any supported source type -> fp32 / bf16, strided rows
 // src element types: 0 bf16, 1 fp16, 2 fp32 (the loader's codes).  rows x cols, destination row pitch ld_dst.
 __device__ __forceinline__ float hy_src_at(const void* src, long long i, int dt) {

@@ -590,7 +590,8 @@ struct AttIo {
   int p_split;   // 1: the softmax weights enter the value product as hi + lo bf16 pairs (fp32-grade weights): twice the PV MMAs
 };
 
-template <int HD, int G>
+// EXT = false compiles the plain causal / windowed kernel (the AttIo options below sink are ignored).
+template <int HD, int G, bool EXT = false>
 __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const bf16* __restrict__ q,
     BatchMeta m, const int* __restrict__ tile_start, const int* __restrict__ tile_len, bf16* __restrict__ out, int H,
@@ -692,14 +693,14 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
       tma_prefetch_desc(&tmV);
       auto issue = [&](const CUtensorMap* tm, uint8_t* dst, uint64_t* bar, int kt, bool wide = false) {
         mbar_expect_tx(bar, Cfg::TILE_BYTES);
-        const int x0 = wide ? (int)blockIdx.z * HD : 0;
+        const int x0 = (EXT && wide) ? (int)blockIdx.z * HD : 0;
         for (int rg = 0; rg < rgs; ++rg) {
           const int i = kt * rgs + rg;
           const int key = tile_of(kt) * XB_ATT_TILE + rg * BR;
           int page;
           if (i < XB_ATT_PG_CACHE) page = s_pages[i];
           else { const int pi = key / P; page = pt[pi < m.max_pages ? pi : m.max_pages - 1]; }
-          const int row = wide ? page * P + (key % P) : (page * KV + kvh) * P + (key % P);
+          const int row = (EXT && wide) ? page * P + (key % P) : (page * KV + kvh) * P + (key % P);
 #pragma unroll
           for (int db = 0; db < HD / 64; ++db) tma_load_2d(dst + db * (XB_ATT_TILE * 128) + rg * BR * 128, tm, bar, x0 + db * 64, row);
         }
@@ -760,7 +761,7 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
           tc_mma_bf16_ts(tm_O, tm_S + (uint32_t)((kt & 1) * XB_ATT_TILE) + ks * 8, umma_desc_mn_sw128(b, XB_ATT_TILE * 128), idesc_o,
                          (kt > 0 || ks > 0) ? 1u : 0u);
           // the low halves of the weights sit in columns 32..63 of the same S buffer
-          if (io.p_split)
+          if (EXT && io.p_split)
             tc_mma_bf16_ts(tm_O, tm_S + (uint32_t)((kt & 1) * XB_ATT_TILE) + 32 + ks * 8, umma_desc_mn_sw128(b, XB_ATT_TILE * 128), idesc_o, 1u);
 #else
           const uint32_t a = p_addr + ks * 32;
@@ -803,7 +804,7 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
     }
     float m_used = -INFINITY;     // reference max (scaled, log2 units) that O and l are expressed against
     float l_sum = 0.f;
-    const float sl2 = io.softcap > 0.f ? 1.0f : scale_log2;                       // what turns a score in v[] into log2 units
+    const float sl2 = (EXT && io.softcap > 0.f) ? 1.0f : scale_log2;                       // what turns a score in v[] into log2 units
     const float cl2 = io.softcap * 1.4426950408889634f;
     const float cap_k = io.softcap > 0.f ? 2.0f * scale_log2 / io.softcap : 0.f;  // raw product -> 2 s / cap in log2 units
     for (int kt = 0; kt < n_kt; ++kt) {
@@ -816,7 +817,7 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
 #pragma unroll
       for (int c = 0; c < XB_ATT_TILE; c += 16) tmem_ld16(tm_Sk + lane_base + c, v + c);
       tmem_ld_wait();
-      if (io.softcap > 0.f) {
+      if (EXT && io.softcap > 0.f) {
         // capped score cap * tanh(s / cap) in place of the raw product, tanh(x) = 1 - 2 / (1 + e^(2x)), already in log2
         // units (cl2 = cap * log2 e), so the softmax below takes it as it is (sl2 = 1): five instructions per score
 #pragma unroll
@@ -898,7 +899,7 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
 #if XB_ATT_P_TMEM
         pw[(c >> 1)] = f2_to_bf2(p[0], p[1]); pw[(c >> 1) + 1] = f2_to_bf2(p[2], p[3]);
         pw[(c >> 1) + 2] = f2_to_bf2(p[4], p[5]); pw[(c >> 1) + 3] = f2_to_bf2(p[6], p[7]);
-        if (io.p_split) {
+        if (EXT && io.p_split) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float2 hi = bf2_to_f2(pw[(c >> 1) + j]);
@@ -906,7 +907,7 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
           }
         }
       }
-      if (io.p_split) {
+      if (EXT && io.p_split) {
         tmem_st16(tm_Sk + lane_base + 32, pl);
         tmem_st16(tm_Sk + lane_base + 48, pl + 16);
       }
@@ -930,10 +931,10 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
     // ---- epilogue: O / l -> bf16 -> attention output row
     mbar_wait(&o_done[(n_kt - 1) & 1], ((n_kt - 1) >> 1) & 1);
     tc_fence_after();
-    if (io.sink != nullptr && m_used != -INFINITY) l_sum += exp2f(io.sink[kvh * G + gq] * 1.4426950408889634f - m_used);
+    if (EXT && io.sink != nullptr && m_used != -INFINITY) l_sum += exp2f(io.sink[kvh * G + gq] * 1.4426950408889634f - m_used);
     const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
-    const long long ohs = io.out_head_stride > 0 ? io.out_head_stride : (long long)HD;
-    bf16* dst = out + ((long long)(t0 + (valid ? tq : 0)) * H + (kvh * G + gq)) * ohs + (io.v_wide ? (long long)blockIdx.z * HD : 0);
+    const long long ohs = (EXT && io.out_head_stride > 0) ? io.out_head_stride : (long long)HD;
+    bf16* dst = out + ((long long)(t0 + (valid ? tq : 0)) * H + (kvh * G + gq)) * ohs + ((EXT && io.v_wide) ? (long long)blockIdx.z * HD : 0);
     const bf16* gate = io.gate != nullptr ? io.gate + (long long)(t0 + (valid ? tq : 0)) * io.ld_gate + (long long)(kvh * G + gq) * HD : nullptr;
 #pragma unroll 1
     for (int c = 0; c < HD; c += 16) {

@@ -972,9 +972,9 @@ template <int HD, int GRP>
 static int hy_attn_tc_any_g(xb_engine* e, const HyLayer& l, const BatchMeta& m, const HyAttnIn& in, bf16* out, int H, int KV, float scale, int gz,
                             cudaStream_t st) {
   using Cfg = AttTcCfg<HD>;
-  XB_SMEM_ATTR_ONCE((xb_attn_prefill_tc_kernel<HD, GRP>), Cfg::SMEM_BYTES);
+  XB_SMEM_ATTR_ONCE((xb_attn_prefill_tc_kernel<HD, GRP, true>), Cfg::SMEM_BYTES);
   e->c.tc_attention++;
-  return hy_launch(e, xb_attn_prefill_tc_kernel<HD, GRP>, dim3(in.n_tiles, KV, gz), dim3(192), Cfg::SMEM_BYTES, st, l.tmK, l.tmV, in.q, m,
+  return hy_launch(e, xb_attn_prefill_tc_kernel<HD, GRP, true>, dim3(in.n_tiles, KV, gz), dim3(192), Cfg::SMEM_BYTES, st, l.tmK, l.tmV, in.q, m,
                    in.tile_start, in.tile_len, out, H, KV, scale * 1.4426950408889634f, AttMask{0, 0}, in.io);
 }
 template <int HD>
@@ -1036,13 +1036,22 @@ static int hy_row_op(xb_engine* e, int T, LinOut m1, float s1, LinOut m2, float 
   a.m3 = hy_none(); a.ha = ha; a.plain_add = 0; a.nw_mode = hy->d.norm_plain ? 1 : 0;
   a.groups = hy->d.norm_groups > 1 ? hy->d.norm_groups : 1;
   a.res_mult = hy->d.residual_mult != 0.f ? hy->d.residual_mult : 1.f;
+  a.ext = (hy->d.norm_plain || a.groups > 1 || a.res_mult != 1.f || ha != nullptr) ? 1 : 0;
   return hy_row_op_launch<AT>(e, T, a, st);
 }
 template <typename AT>
 static int hy_row_op_launch(xb_engine* e, int T, const RowOpArgs& a, cudaStream_t st) {
   HyModel* hy = e->hy;
-  if (T <= 64 && hy->d.dim >= 1024)   // decode-sized batches: few rows, so more threads per row keep more loads in flight
-    return hy_launch(e, hy_row_op_kernel<AT, 1024>, dim3(T), dim3(1024), (size_t)hy->d.dim * sizeof(float), st, a);
+  const bool few = T <= 64 && hy->d.dim >= 1024;   // decode-sized batches: few rows, so more threads per row keep more loads in flight
+  // prompts whose branch is one bf16 matrix out of the tensor-core Linear: eight channels per thread
+  if (!few && !a.plain_add && a.m1.h != nullptr && a.m1.bias == nullptr && a.m1.ld % 8 == 0 && a.m2.f == nullptr && a.m2.h == nullptr &&
+      hy->d.dim % 8 == 0)
+    return hy_launch(e, hy_row_op_vec_kernel<AT>, dim3(T), dim3(256), (size_t)hy->d.dim * sizeof(float), st, a);
+  if (a.ext && !a.plain_add) {   // grouped norms, residual multiplier, plain weights, the norm as a Linear input
+    if (few) return hy_launch(e, hy_row_op_ext_kernel<AT, 1024>, dim3(T), dim3(1024), (size_t)hy->d.dim * sizeof(float), st, a);
+    return hy_launch(e, hy_row_op_ext_kernel<AT, 256>, dim3(T), dim3(256), (size_t)hy->d.dim * sizeof(float), st, a);
+  }
+  if (few) return hy_launch(e, hy_row_op_kernel<AT, 1024>, dim3(T), dim3(1024), (size_t)hy->d.dim * sizeof(float), st, a);
   return hy_launch(e, hy_row_op_kernel<AT, 256>, dim3(T), dim3(256), (size_t)hy->d.dim * sizeof(float), st, a);
 }
 
@@ -1180,7 +1189,7 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
   auto row_op = [&](LinOut y1, LinOut y2, const float* nw) -> int {
     RowOpArgs a;
     a.x = hy->x; a.m1 = y1; a.m2 = y2; a.m3 = hy_none(); a.s1 = 1.f; a.s2 = 1.f; a.bw = nullptr; a.bw_one = 0.f; a.nw = nw; a.hn = hy->hn;
-    a.xa = nullptr; a.ha = hy->ah; a.eps = d.norm_eps; a.D = D; a.plain_add = 1; a.nw_mode = nwm; a.groups = 1; a.res_mult = 1.f;
+    a.xa = nullptr; a.ha = hy->ah; a.eps = d.norm_eps; a.D = D; a.plain_add = 1; a.nw_mode = nwm; a.groups = 1; a.res_mult = 1.f; a.ext = 0;
     return hy_row_op_launch<AT>(e, T, a, st);
   };
   XB_TRY(hy_launch(e, hy_embed_kernel, dim3(T), dim3(128), 0, st, (const int*)e->in_tokens, (const bf16*)hy->embed, hy->x, D, d.vocab,
@@ -1466,7 +1475,7 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
       s2 = c.right_scale;
     }
     // x += norm1b(mixer); then whatever reads x next
-    const bool ff_direct = has_ff && (d.ff_unfiltered || d.taps == 0);   // the feed-forward reads its norm without a filter
+    const bool ff_direct = has_ff && d.ff_unfiltered != 0;   // the feed-forward reads its norm without a filter
     XB_TRY(hy_row_op<AT>(e, T, y1, s1, y2, s2, l.norm1b, 1.f, has_ff ? l.norm2 : (has_side ? nullptr : next_norm),
                          (!has_ff && has_side && !side_fused) ? (void*)a1 : nullptr, st, ff_direct ? (void*)a1 : nullptr));
     if (has_ff && c.ff_kind == XB_FF_MOE) {

@@ -110,8 +110,10 @@ struct RowOpArgs {
   float eps;
   int D;
   int plain_add, nw_mode;
+  // read by hy_row_op_ext_kernel / hy_row_op_vec_kernel only:
   int groups;       // > 1: every norm divides each of `groups` equal consecutive parts of the row by its own root mean square
   float res_mult;   // the normed branch is multiplied by this before it joins the stream
+  int ext;          // the sandwich wrapper sets it when a model uses any of: groups, res_mult, plain weights, ha
 };
 #define HY_MAX_NORM_GROUPS 64
 // 1 / sqrt(mean(part^2) + eps) of each part of row[0, D) into ginv: a warp per part, lanes stride the part (a fixed order,
@@ -143,34 +145,7 @@ __global__ void __launch_bounds__(NT) hy_row_op_kernel(RowOpArgs a) {
   float* x = a.x + t * D;
   const bool branch = a.m1.f != nullptr || a.m1.h != nullptr;
   const bool two = a.m2.f != nullptr || a.m2.h != nullptr;
-  if (a.groups > 1) {
-    // grouped norms (sandwich form): x += res_mult * gnorm(branch) * bw;  hn = gnorm(x) * nw
-    __shared__ float ginv[HY_MAX_NORM_GROUPS];
-    const int gs = D / a.groups;
-    if (branch) {
-      for (int i = threadIdx.x; i < D; i += NT) {
-        float v = a.s1 * lin_at(a.m1, t, i);
-        if (two) v += a.s2 * lin_at(a.m2, t, i);
-        row[i] = v;
-      }
-      hy_group_inv(row, D, a.groups, a.eps, ginv);
-      for (int i = threadIdx.x; i < D; i += NT) {
-        const float v = x[i] + a.res_mult * (row[i] * ginv[i / gs] * (a.bw[i] + a.bw_one));
-        x[i] = v;
-        row[i] = v;
-      }
-    } else {
-      for (int i = threadIdx.x; i < D; i += NT) row[i] = x[i];
-    }
-    if (a.nw != nullptr) {
-      hy_group_inv(row, D, a.groups, a.eps, ginv);
-      for (int i = threadIdx.x; i < D; i += NT) {
-        const float v = row[i] * ginv[i / gs] * hy_norm_weight(a.nw, a.nw_mode, i);
-        a.hn[t * D + i] = v;
-        if (a.ha != nullptr) act_store<AT>(reinterpret_cast<AT*>(a.ha) + t * D + i, v);
-      }
-    }
-  } else if (branch && a.plain_add) {
+  if (branch && a.plain_add) {
     const bool three = a.m3.f != nullptr || a.m3.h != nullptr;
     float s2 = 0.f;
     for (int i = threadIdx.x; i < D; i += NT) {
@@ -204,7 +179,7 @@ __global__ void __launch_bounds__(NT) hy_row_op_kernel(RowOpArgs a) {
     const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
     float s2 = 0.f;
     for (int i = threadIdx.x; i < D; i += NT) {
-      const float v = x[i] + a.res_mult * (row[i] * inv * (a.bw[i] + a.bw_one));
+      const float v = x[i] + row[i] * inv * (a.bw[i] + a.bw_one);
       x[i] = v;
       row[i] = v;
       s2 += v * v;
@@ -213,11 +188,7 @@ __global__ void __launch_bounds__(NT) hy_row_op_kernel(RowOpArgs a) {
     s2 = block_sum<NT>(s2, red);
     if (a.nw != nullptr) {
       const float inv2 = 1.0f / sqrtf(s2 / (float)D + a.eps);
-      for (int i = threadIdx.x; i < D; i += NT) {
-        const float v = row[i] * inv2 * hy_norm_weight(a.nw, a.nw_mode, i);
-        a.hn[t * D + i] = v;
-        if (a.ha != nullptr) act_store<AT>(reinterpret_cast<AT*>(a.ha) + t * D + i, v);
-      }
+      for (int i = threadIdx.x; i < D; i += NT) a.hn[t * D + i] = row[i] * inv2 * (1.0f + a.nw[i]);
     }
   } else {
     float s2 = 0.f;
@@ -243,6 +214,129 @@ __global__ void __launch_bounds__(NT) hy_row_op_kernel(RowOpArgs a) {
   if (a.xa != nullptr) {
     AT* xa = reinterpret_cast<AT*>(a.xa) + t * D;
     for (int i = threadIdx.x; i < D; i += NT) act_store<AT>(xa + i, row[i]);
+  }
+}
+
+// The sandwich form with the options a design may set beside Refatar's: norms in `groups` parts, a multiplier on the normed
+// branch, plain or offset weights (bw_one / nw_mode), the next reader's norm also as a Linear input (ha).
+//   x += res_mult * gnorm(s1 m1 + s2 m2) * (bw + bw_one);  hn = gnorm(x) * weight(nw);  ha = hn;  xa = x
+template <typename AT, int NT>
+__global__ void __launch_bounds__(NT) hy_row_op_ext_kernel(RowOpArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row[];
+  __shared__ float ginv[HY_MAX_NORM_GROUPS];
+  const long long t = blockIdx.x;
+  const int D = a.D, groups = a.groups > 1 ? a.groups : 1, gs = D / groups;
+  float* x = a.x + t * D;
+  const bool branch = a.m1.f != nullptr || a.m1.h != nullptr;
+  const bool two = a.m2.f != nullptr || a.m2.h != nullptr;
+  if (branch) {
+    for (int i = threadIdx.x; i < D; i += NT) {
+      float v = a.s1 * lin_at(a.m1, t, i);
+      if (two) v += a.s2 * lin_at(a.m2, t, i);
+      row[i] = v;
+    }
+    hy_group_inv(row, D, groups, a.eps, ginv);
+    for (int i = threadIdx.x; i < D; i += NT) {
+      const float v = x[i] + a.res_mult * (row[i] * ginv[i / gs] * (a.bw[i] + a.bw_one));
+      x[i] = v;
+      row[i] = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < D; i += NT) row[i] = x[i];
+  }
+  if (a.nw != nullptr) {
+    hy_group_inv(row, D, groups, a.eps, ginv);
+    for (int i = threadIdx.x; i < D; i += NT) {
+      const float v = row[i] * ginv[i / gs] * hy_norm_weight(a.nw, a.nw_mode, i);
+      a.hn[t * D + i] = v;
+      if (a.ha != nullptr) act_store<AT>(reinterpret_cast<AT*>(a.ha) + t * D + i, v);
+    }
+  }
+  if (a.xa != nullptr) {
+    __syncthreads();
+    AT* xa = reinterpret_cast<AT*>(a.xa) + t * D;
+    for (int i = threadIdx.x; i < D; i += NT) act_store<AT>(xa + i, row[i]);
+  }
+}
+
+// The sandwich form for prompts whose branch is ONE bf16 matrix (the tensor-core Linear's output, no bias): the same
+// arithmetic as hy_row_op_kernel with eight neighbouring channels per thread (16-byte loads of the branch, 32-byte loads and
+// stores of the stream).  D, the branch's row pitch: multiples of 8.  One block of 256 threads per row.
+__device__ __forceinline__ void hy_load8(const bf16* p, const float* bias, float* v);   // eight bf16 neighbours as floats (below)
+__device__ __forceinline__ void hy_ld8f(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void hy_st8f(float* p, const float* v) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <typename AT> __device__ __forceinline__ void hy_st8a(AT* p, const float* v);
+template <> __device__ __forceinline__ void hy_st8a<float>(float* p, const float* v) { hy_st8f(p, v); }
+template <> __device__ __forceinline__ void hy_st8a<bf16>(bf16* p, const float* v) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(f2_to_bf2(v[0], v[1]), f2_to_bf2(v[2], v[3]), f2_to_bf2(v[4], v[5]), f2_to_bf2(v[6], v[7]));
+}
+template <typename AT>
+__global__ void __launch_bounds__(256) hy_row_op_vec_kernel(RowOpArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int NT = 256;
+  extern __shared__ __align__(16) float row[];
+  __shared__ float red[32];
+  __shared__ float ginv[HY_MAX_NORM_GROUPS];
+  const long long t = blockIdx.x;
+  const int D = a.D, groups = a.groups > 1 ? a.groups : 1, gs = D / groups;
+  float* x = a.x + t * D;
+  const bf16* br = a.m1.h + t * a.m1.ld;
+  // branch -> row[], its norm
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < D; i += NT * 8) {
+    float v[8];
+    hy_load8(br + i, nullptr, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { v[j] *= a.s1; ss = fmaf(v[j], v[j], ss); }
+    hy_st8f(row + i, v);
+  }
+  float inv = 0.f;
+  if (groups > 1) hy_group_inv(row, D, groups, a.eps, ginv);
+  else inv = 1.0f / sqrtf(block_sum<NT>(ss, red) / (float)D + a.eps);
+  // x += res_mult * normed branch * weight; row[] <- x
+  ss = 0.f;
+  for (int i = threadIdx.x * 8; i < D; i += NT * 8) {
+    float v[8], xv[8], w[8];
+    hy_ld8f(row + i, v);
+    hy_ld8f(x + i, xv);
+    hy_ld8f(a.bw + i, w);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float iv = groups > 1 ? ginv[(i + j) / gs] : inv;
+      xv[j] = xv[j] + a.res_mult * (v[j] * iv * (w[j] + a.bw_one));
+      ss = fmaf(xv[j], xv[j], ss);
+    }
+    hy_st8f(x + i, xv);
+    hy_st8f(row + i, xv);
+  }
+  if (a.nw != nullptr) {
+    if (groups > 1) hy_group_inv(row, D, groups, a.eps, ginv);
+    else inv = 1.0f / sqrtf(block_sum<NT>(ss, red) / (float)D + a.eps);
+    for (int i = threadIdx.x * 8; i < D; i += NT * 8) {
+      float v[8];
+      hy_ld8f(row + i, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = v[j] * (groups > 1 ? ginv[(i + j) / gs] : inv) * hy_norm_weight(a.nw, a.nw_mode, i + j);
+      hy_st8f(a.hn + t * D + i, v);
+      if (a.ha != nullptr) hy_st8a<AT>(reinterpret_cast<AT*>(a.ha) + t * D + i, v);
+    }
+  }
+  if (a.xa != nullptr) {
+    if (a.nw == nullptr) __syncthreads();
+    for (int i = threadIdx.x * 8; i < D; i += NT * 8) {
+      float v[8];
+      hy_ld8f(row + i, v);
+      hy_st8a<AT>(reinterpret_cast<AT*>(a.xa) + t * D + i, v);
+    }
   }
 }
 
@@ -1134,7 +1228,6 @@ __global__ void __launch_bounds__(256) hy_rope_append_kernel(LinOut P, int off_q
 // the tensor-core Linear left (no bias), queries leave as bf16 rows for the tensor-core attention.  Wants dk, dv, the row pitch
 // and the column offsets to be multiples of 8, and the rotating part a multiple of 8 entries (pairs (2i, 2i+1)) or of 16
 // (pairs (i, i + dims/2): a thread turns the 8 entries at d together with the 8 at d + dims/2).  grid (T), 256 threads.
-__device__ __forceinline__ void hy_load8(const bf16* p, const float* bias, float* v);   // eight bf16 neighbours as floats (below)
 __device__ __forceinline__ uint4 hy_pack8(const float* y) {
   return make_uint4(f2_to_bf2(y[0], y[1]), f2_to_bf2(y[2], y[3]), f2_to_bf2(y[4], y[5]), f2_to_bf2(y[6], y[7]));
 }

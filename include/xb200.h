@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define XB_ABI_VERSION 7
+#define XB_ABI_VERSION 8
 
 typedef struct xb_engine xb_engine;
 
@@ -239,7 +239,12 @@ enum {
                           softmax denominator (s_sink), scores squashed to cap * tanh(score / cap) (s_softcap), the
                           normalised weights of the heads mixed by an [H, H] matrix before they meet the values (s_talk),
                           values blended with those of the first blending layer, v <- (1 - l) v + l v_first (s_vmix),
-                          one sigmoid output gate per head (s_gate) */
+                          one sigmoid output gate per head (s_gate); biases on the q / k (/ v) projections (s_qkv_bias);
+                          queries and keys RMS-normed over the whole projection, all heads at once, with a weight per
+                          channel (s_qk_norm); values that are the keys as projected, before that norm, with no value
+                          projection (s_v_is_k); queries multiplied by 1 + coef ln(floor((pos + 1) / every) + 1)
+                          (s_qtemp_*); r1_h ln(1 + r2_h (i - j)) taken off the score of query i and key j, two numbers
+                          per head (s_dist_bias) */
 };
 
 /* how the rotary frequencies f_i = base^(-2i/dims) of XB_MIX_SOFTMAX are rescaled (l_i = 2 pi / f_i) */
@@ -263,8 +268,15 @@ enum {
 /* what an expert of XB_FF_MOE computes (ff_act) */
 enum {
   XB_ACT_GLU_CLAMP = 0,   /* down(g sigmoid(1.702 g) (u + 1)) with the limits above */
-  XB_ACT_SWIGLU = 1       /* down(silu(g) u), no limits */
+  XB_ACT_SWIGLU = 1,      /* down(silu(g) u), no limits */
+  XB_ACT_GELU = 2         /* down(gelu(up h)): no gate projection, the exact (erf) form 0.5 z (1 + erf(z / sqrt 2)) */
 };
+/* how the router of XB_FF_MOE turns logits into scores, what a group of experts is worth, and what weight a chosen expert
+ * gets (route_score, group_score, route_norm) */
+enum { XB_ROUTE_SIGMOID = 0, XB_ROUTE_SOFTMAX = 1 };   /* scores = sigmoid(z) / softmax(z) over all experts */
+enum { XB_GROUP_TOP2 = 0, XB_GROUP_MAX = 1 };          /* group score = sum of its two best scores / its best score */
+enum { XB_SINK_NONE = 0, XB_SINK_LEARNED = 1, XB_SINK_UNIT = 2 };  /* s_sink: none / tensor "sink" per head / score 0: the
+                                                                      softmax denominator gets one more unit */
 
 typedef struct xb_hybrid_layer {
   int32_t mixer;                                    /* XB_MIX_* */
@@ -297,6 +309,12 @@ typedef struct xb_hybrid_layer {
                                                        that sets this (which keeps its own as they are) */
   float s_scale, s_softcap, s_rot_mult;             /* score = q.k * s_scale; cap 0 = none; cos / sin multiplier */
   double s_rot_base, s_rot_factor, s_rot_orig, s_rot_p0, s_rot_p1;
+  int32_t s_qkv_bias, s_qk_norm, s_v_is_k, s_dist_bias;   /* 0 / 1 each (XB_MIX_SOFTMAX, see there) */
+  int32_t s_qtemp_every;                            /* query temperature: positions per step of the logarithm; 0 = none */
+  float s_qtemp_coef;
+  int32_t route_score, group_score;                 /* XB_FF_MOE: XB_ROUTE_*, XB_GROUP_* */
+  int32_t route_norm;                               /* XB_FF_MOE: 1 = the chosen experts' weights are their scores divided by
+                                                       the sum of the chosen scores (+ 1e-20), then times route_scale */
 } xb_hybrid_layer;
 
 typedef struct xb_hybrid_desc {
@@ -319,12 +337,23 @@ typedef struct xb_hybrid_desc {
   int32_t tied_head;                 /* 1: the logits are products with the embedding table itself (no "head" tensor) */
   int32_t ff_unfiltered;             /* sandwich blocks: 1 = only the mixer reads through the causal filter ("canon1"); the
                                         feed-forward reads its norm directly */
+  int32_t gated_residual;            /* branch-norm blocks: 1 = a sublayer's output is multiplied, channel by channel, by
+                                        sigmoid(W x + b) of what the sublayer read ("l<i>.rg1" / ".rg1.b", "rg2" for the
+                                        feed-forward) before its norm */
+  int32_t bigram_buckets;            /* > 0: row (prev * bigram_mul_prev + token * bigram_mul_cur) mod buckets of the table
+                                        "bigram" [buckets + 1, dim] joins the embedding; a sequence's first token takes the
+                                        last row.  The previous token of a sequence is part of its slot's state */
+  int32_t bigram_mul_prev, bigram_mul_cur;
+  int32_t pos_rows;                  /* > 0: row `position` of the learned table "pos" [pos_rows, dim] joins the embedding */
 } xb_hybrid_desc;
 
 enum {
   XB_BLOCK_SANDWICH = 0,  /* mixer, then feed-forward, each reading its own norm through a causal filter, each branch
                              normed before it is added; optional token side input (the Refatar layout) */
-  XB_BLOCK_PARALLEL = 1   /* one norm per layer; mixer and feed-forward read it and their sum is added: x += mix(h) + ff(h) */
+  XB_BLOCK_PARALLEL = 1,  /* one norm per layer; mixer and feed-forward read it and their sum is added: x += mix(h) + ff(h) */
+  XB_BLOCK_BRANCHNORM = 2 /* no norm in front: each sublayer reads the stream itself and only its output is normed,
+                             x += n1 unit(mix(x)), then x += n2 unit(ff(x)), unit(y) = y / rms(y), n1 / n2 single numbers
+                             ("l<i>.norm1", ".norm2"; norm_scalar = 1); optional sigmoid gate on the output (gated_residual) */
 };
 
 int xb_engine_create_hybrid(const xb_hybrid_desc* desc, const xb_hybrid_layer* layers, int device, xb_engine** out);

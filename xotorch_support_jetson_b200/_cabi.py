@@ -37,7 +37,7 @@ class ModelDesc(C.Structure):
   ]
 
 
-ABI_VERSION = 7
+ABI_VERSION = 8
 
 
 def model_desc(**fields) -> ModelDesc:
@@ -47,9 +47,12 @@ def model_desc(**fields) -> ModelDesc:
 
 MIX_DELTA, MIX_PARALLEL, MIX_LATENT, MIX_GDELTA, MIX_LIGHTNING, MIX_SOFTMAX = 1, 2, 3, 4, 5, 6
 ROT_SCALE_NONE, ROT_SCALE_BANDS, ROT_SCALE_RAMP = 0, 1, 2
-ACT_GLU_CLAMP, ACT_SWIGLU = 0, 1
+ACT_GLU_CLAMP, ACT_SWIGLU, ACT_GELU = 0, 1, 2
+ROUTE_SIGMOID, ROUTE_SOFTMAX = 0, 1
+GROUP_TOP2, GROUP_MAX = 0, 1
+SINK_NONE, SINK_LEARNED, SINK_UNIT = 0, 1, 2
 FF_RELU2, FF_GLU_CLAMP, FF_MOE = 0, 1, 2
-BLOCK_SANDWICH, BLOCK_PARALLEL = 0, 1
+BLOCK_SANDWICH, BLOCK_PARALLEL, BLOCK_BRANCHNORM = 0, 1, 2
 ST_BF16, ST_F16, ST_F32 = 0, 1, 2   # element types xb_load_named accepts
 
 
@@ -75,6 +78,9 @@ class HybridLayer(C.Structure):
     ("s_scale", C.c_float), ("s_softcap", C.c_float), ("s_rot_mult", C.c_float),
     ("s_rot_base", C.c_double), ("s_rot_factor", C.c_double), ("s_rot_orig", C.c_double), ("s_rot_p0", C.c_double),
     ("s_rot_p1", C.c_double),
+    ("s_qkv_bias", C.c_int32), ("s_qk_norm", C.c_int32), ("s_v_is_k", C.c_int32), ("s_dist_bias", C.c_int32),
+    ("s_qtemp_every", C.c_int32), ("s_qtemp_coef", C.c_float),
+    ("route_score", C.c_int32), ("group_score", C.c_int32), ("route_norm", C.c_int32),
   ]
 
 
@@ -87,6 +93,8 @@ class HybridDesc(C.Structure):
     ("block", C.c_int32), ("norm_scalar", C.c_int32), ("embed_scale", C.c_float),
     ("norm_groups", C.c_int32), ("norm_plain", C.c_int32), ("residual_mult", C.c_float), ("tied_head", C.c_int32),
     ("ff_unfiltered", C.c_int32),
+    ("gated_residual", C.c_int32), ("bigram_buckets", C.c_int32), ("bigram_mul_prev", C.c_int32), ("bigram_mul_cur", C.c_int32),
+    ("pos_rows", C.c_int32),
   ]
 
 

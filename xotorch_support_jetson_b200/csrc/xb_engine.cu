@@ -1297,9 +1297,13 @@ extern "C" int xb_engine_create_hybrid(const xb_hybrid_desc* desc, const xb_hybr
   XB_CHECK(h.dim <= 12288, "dim %d: the row kernels keep a row in 48 KB of shared memory (<= 12288)", h.dim);
   XB_CHECK(h.taps >= 0 && h.taps <= HY_MAX_TAPS && h.side_dim >= 0, "bad taps %d (0..%d) / side_dim %d", h.taps, HY_MAX_TAPS, h.side_dim);
   XB_CHECK(h.max_batch_tokens > 0 && h.max_seqs > 0 && h.max_logit_rows >= 0, "max_batch_tokens / max_seqs must be > 0");
-  XB_CHECK(h.block == XB_BLOCK_SANDWICH || h.block == XB_BLOCK_PARALLEL, "unknown block layout %d", h.block);
-  XB_CHECK(h.block == XB_BLOCK_SANDWICH || (h.taps == 0 && h.side_dim == 0), "parallel blocks carry no causal filter or token side input");
-  XB_CHECK(h.block == XB_BLOCK_PARALLEL || h.norm_scalar == 0, "sandwich blocks carry a norm weight per channel");
+  XB_CHECK(h.block == XB_BLOCK_SANDWICH || h.block == XB_BLOCK_PARALLEL || h.block == XB_BLOCK_BRANCHNORM, "unknown block layout %d", h.block);
+  XB_CHECK(h.block == XB_BLOCK_SANDWICH || (h.taps == 0 && h.side_dim == 0), "only sandwich blocks carry a causal filter or a token side input");
+  XB_CHECK(h.block != XB_BLOCK_SANDWICH || h.norm_scalar == 0, "sandwich blocks carry a norm weight per channel");
+  XB_CHECK(h.block == XB_BLOCK_BRANCHNORM || (h.gated_residual == 0 && h.bigram_buckets == 0 && h.pos_rows == 0),
+           "a gated residual, a token-pair table and a learned position table are options of branch-norm blocks");
+  XB_CHECK(h.bigram_buckets >= 0 && h.pos_rows >= 0 && (h.bigram_buckets == 0 || (h.bigram_mul_prev >= 0 && h.bigram_mul_cur >= 0)),
+           "bad token-pair table constants (%d buckets, multipliers %d / %d) or position rows %d", h.bigram_buckets, h.bigram_mul_prev, h.bigram_mul_cur, h.pos_rows);
   XB_CHECK(h.norm_groups >= 0 && h.norm_groups <= HY_MAX_NORM_GROUPS && (h.norm_groups <= 1 || h.dim % h.norm_groups == 0),
            "norm groups %d must divide dim %d (at most %d)", h.norm_groups, h.dim, HY_MAX_NORM_GROUPS);
   XB_CHECK(h.block == XB_BLOCK_SANDWICH || (h.norm_groups <= 1 && h.norm_plain == 0 && (h.residual_mult == 0.f || h.residual_mult == 1.f) && h.ff_unfiltered == 0),
@@ -1314,7 +1318,7 @@ extern "C" int xb_engine_create_hybrid(const xb_hybrid_desc* desc, const xb_hybr
   e->d.dim = h.dim;
   e->d.vocab = h.vocab;
   e->d.norm_eps = h.norm_eps;
-  e->d.max_positions = 1 << 30;   // no rotation table bounds the positions
+  e->d.max_positions = h.pos_rows > 0 ? h.pos_rows : 1 << 30;   // only a learned position table bounds the positions
   e->d.max_batch_tokens = h.max_batch_tokens;
   e->d.max_seqs = h.max_seqs;
   e->device = device;

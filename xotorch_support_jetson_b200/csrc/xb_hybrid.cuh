@@ -48,12 +48,18 @@ struct HyLayer {
   double* rot_freq_d = nullptr;             // [s_rot_dims / 2] rescaled frequencies
   int vmode = 0;                            // 0: values as projected; 1: leaves its values for later layers; 2: blends with them
   bool v_all = false;                       // a value row of the pool holds every key head ([page][token][G * dv])
+  // whole-projection q / k norm weights, the distance penalty's two numbers per head (XB_MIX_SOFTMAX options)
+  float *qn = nullptr, *kn = nullptr, *r1 = nullptr, *r2 = nullptr;
+  // gated residual: the gate's rows sit behind the mixer's in w_in (off_rg) and behind the experts' in w_up (off_rg2)
+  int off_rg = -1, off_rg2 = -1;
 };
 
 struct HyModel {
   xb_hybrid_desc d{};
   std::vector<HyLayer> L;
   bf16 *embed = nullptr, *side_embed = nullptr, *head = nullptr;
+  bf16 *bigram = nullptr, *pos_tab = nullptr;   // hashed token-pair rows [buckets + 1, dim], learned position rows [pos_rows, dim]
+  size_t st_prev = 0;                           // float offset of a slot's previous token (its bits) inside the slot's state
   float* final_norm = nullptr;
   float* state = nullptr;
   size_t state_floats = 0;   // per slot
@@ -153,9 +159,11 @@ static int hy_create_mixer(xb_engine* e, int i, bool own, size_t& st, uint64_t& 
              c.m_rot_dims, dr);
     l.off_q = 0; l.off_dkv = (int)(H * (n + dr));
     l.n_in = l.off_dkv + (int)(R + dr);
+    if (d.gated_residual) { l.off_rg = l.n_in; l.n_in += (int)D; }
     l.n_o = (int)(H * dv);
     if (own) {
       XB_TRY(hy_alloc_t(hy, &l.w_in, (size_t)l.n_in * D));
+      if (d.gated_residual) XB_TRY(hy_alloc_t(hy, &l.b_in, (size_t)l.n_in));
       XB_TRY(hy_alloc_t(hy, &l.w_o, D * l.n_o));
       XB_TRY(hy_alloc_t(hy, &l.w_uk, (size_t)(H * n * R)));
       XB_TRY(hy_alloc_t(hy, &l.w_uv, (size_t)(H * dv * R)));
@@ -248,25 +256,48 @@ static int hy_create_softmax(xb_engine* e, int i, bool own, uint64_t& wbytes, ui
   const std::string p = "l" + std::to_string(i) + ".mix.";
   const long long H = c.s_heads, G = c.s_kv_heads, dk = c.s_dim, dv = c.s_vdim, rd = c.s_rot_dims;
   XB_CHECK(own, "layer %d: an attention layer keeps tensors of its own", i);
-  XB_CHECK(d.block == XB_BLOCK_SANDWICH, "layer %d: rotary-position attention belongs to sandwich blocks", i);
+  XB_CHECK(d.block == XB_BLOCK_SANDWICH || d.block == XB_BLOCK_BRANCHNORM, "layer %d: softmax attention belongs to sandwich or branch-norm blocks", i);
   XB_CHECK(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0, "layer %d: bad attention sizes", i);
+  const bool vk = c.s_v_is_k != 0;
+  const bool prep2 = c.s_qk_norm != 0 || vk || c.s_qtemp_every > 0;   // hy_qk_prep_kernel in place of the rotation kernel
+  XB_CHECK(!vk || (dv == dk && !c.s_vmix && !c.s_talk), "layer %d: values that are the keys need equal sizes and neither blending nor mixed heads", i);
+  XB_CHECK(!prep2 || (rd == 0 && !c.s_vmix && !c.s_talk), "layer %d: whole-projection norms, key values and the query temperature come without rotation, blending or mixed heads", i);
+  XB_CHECK(!prep2 || (size_t)((H + G) * dk) * sizeof(float) <= 48 * 1024, "layer %d: %lld query and key channels per token (at most 12288)", i, (H + G) * dk);
+  XB_CHECK(c.s_qtemp_every >= 0 && c.s_sink >= XB_SINK_NONE && c.s_sink <= XB_SINK_UNIT, "layer %d: bad query temperature step %d / sink kind %d", i, c.s_qtemp_every, c.s_sink);
   XB_CHECK(rd >= 0 && rd <= dk && rd % 2 == 0, "layer %d: %lld rotating entries do not fit a head of %lld", i, rd, dk);
   XB_CHECK(rd / 2 <= HY_MAX_ROT_PAIRS, "layer %d: %lld rotating entries (at most %d)", i, rd, 2 * HY_MAX_ROT_PAIRS);
   XB_CHECK(c.s_rot_pairs == XB_ROPE_INTERLEAVED || c.s_rot_pairs == XB_ROPE_HALF_SPLIT, "layer %d: unknown rotary pair layout %d", i, c.s_rot_pairs);
   XB_CHECK(c.s_softcap >= 0.f && c.s_scale > 0.f, "layer %d: bad score scale %g / soft cap %g", i, c.s_scale, c.s_softcap);
   l.v_all = c.s_talk != 0 && G > 1;
   const long long dvo = l.v_all ? G * dv : dv;   // value channels one (token, head) block of the attention kernel carries
-  l.off_q = 0; l.off_k = (int)(H * dk); l.off_v = l.off_k + (int)(G * dk); l.off_g = l.off_v + (int)(G * dv);
+  // values that are the keys as projected: no value rows, the value columns ARE the key columns
+  l.off_q = 0; l.off_k = (int)(H * dk); l.off_v = vk ? l.off_k : l.off_k + (int)(G * dk); l.off_g = l.off_v + (int)(G * dv);
   l.n_in = l.off_g + (c.s_gate ? (int)H : 0);
+  if (d.gated_residual) { l.off_rg = l.n_in; l.n_in += (int)D; }
   l.n_o = (int)(H * dv);
   XB_TRY(hy_alloc_t(hy, &l.w_in, (size_t)l.n_in * D));
   XB_TRY(hy_alloc_t(hy, &l.w_o, D * l.n_o));
   hy_name_rows(hy, p + "q", l.w_in, l.off_q, H * dk, D);
   hy_name_rows(hy, p + "k", l.w_in, l.off_k, G * dk, D);
-  hy_name_rows(hy, p + "v", l.w_in, l.off_v, G * dv, D);
+  if (!vk) hy_name_rows(hy, p + "v", l.w_in, l.off_v, G * dv, D);
   if (c.s_gate) hy_name_rows(hy, p + "g", l.w_in, l.off_g, H, D);
   hy_name_rows(hy, p + "o", l.w_o, 0, D, l.n_o);
-  if (c.s_sink) { XB_TRY(hy_alloc_t(hy, &l.sink, (size_t)H)); hy_name_vec(hy, p + "sink", l.sink, H); }
+  if (c.s_qkv_bias || d.gated_residual) XB_TRY(hy_alloc_t(hy, &l.b_in, (size_t)l.n_in));
+  if (c.s_qkv_bias) {
+    hy_name_vec(hy, p + "q.b", l.b_in + l.off_q, H * dk);
+    hy_name_vec(hy, p + "k.b", l.b_in + l.off_k, G * dk);
+    if (!vk) hy_name_vec(hy, p + "v.b", l.b_in + l.off_v, G * dv);
+  }
+  if (c.s_qk_norm) {
+    XB_TRY(hy_alloc_t(hy, &l.qn, (size_t)(H * dk))); hy_name_vec(hy, p + "q.norm", l.qn, H * dk);
+    XB_TRY(hy_alloc_t(hy, &l.kn, (size_t)(G * dk))); hy_name_vec(hy, p + "k.norm", l.kn, G * dk);
+  }
+  if (c.s_dist_bias) {
+    XB_TRY(hy_alloc_t(hy, &l.r1, (size_t)H)); hy_name_vec(hy, p + "r1", l.r1, H);
+    XB_TRY(hy_alloc_t(hy, &l.r2, (size_t)H)); hy_name_vec(hy, p + "r2", l.r2, H);
+  }
+  if (c.s_sink == XB_SINK_LEARNED) { XB_TRY(hy_alloc_t(hy, &l.sink, (size_t)H)); hy_name_vec(hy, p + "sink", l.sink, H); }
+  if (c.s_sink == XB_SINK_UNIT) XB_TRY(hy_alloc_t(hy, &l.sink, (size_t)H));   // a sink of score 0 per head: the zeros the allocation leaves
   if (c.s_talk) { XB_TRY(hy_alloc_t(hy, &l.talk, (size_t)(H * H))); hy_name(hy, p + "talk", l.talk, true, H, H, H, 2); }
   if (c.s_vmix) { XB_TRY(hy_alloc_t(hy, &l.vmix, 1)); hy_name_vec(hy, p + "vmix", l.vmix, 1); }
   // frequencies f_j = base^(-2j/dims), rescaled (xb200.h: XB_ROT_SCALE_*)
@@ -308,7 +339,8 @@ static int hy_create_softmax(xb_engine* e, int i, bool own, uint64_t& wbytes, ui
   if (c.s_vmix && (size_t)(G * dv) > hy->maxGV) hy->maxGV = (size_t)(G * dv);
   // bf16 serving, key and value heads of one size (64 or 128), at most 8 query heads per key head: prompts run through the
   // engine's tcgen05 attention (sink, score cap and the wide value rows of mixed heads as its options)
-  l.tc_attn = !d.compute_fp32 && dk == dv && (dk == 64 || dk == 128) && H / G <= 8;
+  // (the tensor-core kernels know no distance penalty: such layers run the per-(token, head) kernel)
+  l.tc_attn = !d.compute_fp32 && dk == dv && (dk == 64 || dk == 128) && H / G <= 8 && !c.s_dist_bias;
   if (l.tc_attn && qa > hy->maxQG) hy->maxQG = qa;
   wbytes += ((size_t)l.n_in * D + D * l.n_o) * 2;
   kvpos += (uint64_t)G * (dk + dv) * (d.compute_fp32 ? 4 : 2);
@@ -324,7 +356,11 @@ static int hy_create_ff(xb_engine* e, int i, bool own, uint64_t& wbytes) {
   const size_t D = hy->d.dim, F = c.ff;
   const std::string p = "l" + std::to_string(i) + ".mlp.";
   XB_CHECK(hy->d.block == XB_BLOCK_PARALLEL || c.ff_kind == XB_FF_MOE, "layer %d: the dense gated feed-forward belongs to parallel blocks", i);
-  XB_CHECK(c.ff_act == XB_ACT_GLU_CLAMP || c.ff_act == XB_ACT_SWIGLU, "layer %d: unknown expert activation %d", i, c.ff_act);
+  XB_CHECK(c.ff_act == XB_ACT_GLU_CLAMP || c.ff_act == XB_ACT_SWIGLU || c.ff_act == XB_ACT_GELU, "layer %d: unknown expert activation %d", i, c.ff_act);
+  XB_CHECK(c.ff_act != XB_ACT_GELU || (c.ff_kind == XB_FF_MOE && !c.route_input), "layer %d: the ungated GELU form serves experts weighted on their output", i);
+  XB_CHECK((c.route_score == XB_ROUTE_SIGMOID || c.route_score == XB_ROUTE_SOFTMAX) && (c.group_score == XB_GROUP_TOP2 || c.group_score == XB_GROUP_MAX),
+           "layer %d: unknown router score %d / group score %d", i, c.route_score, c.group_score);
+  const bool rg = hy->d.gated_residual != 0;
   if (c.ff_kind == XB_FF_GLU_CLAMP) {
     l.n_up = (int)(2 * F); l.n_dn = (int)F;
     if (own) {
@@ -342,7 +378,10 @@ static int hy_create_ff(xb_engine* e, int i, bool own, uint64_t& wbytes) {
     XB_CHECK(c.groups == 0 || (c.groups > 0 && E % c.groups == 0 && c.keep_groups > 0 && c.keep_groups <= c.groups &&
                                (size_t)c.top <= (E / c.groups) * c.keep_groups),
              "layer %d: %d groups (%d kept) do not fit %d experts with %d per token", i, c.groups, c.keep_groups, c.n_experts, c.top);
-    l.n_up = (int)(2 * (E * F + S)); l.n_dn = (int)(E * F + S);
+    const bool gated = c.ff_act != XB_ACT_GELU;   // ungated experts: up rows only, expert after expert, then the shared expert's
+    const size_t U = gated ? 2 : 1;
+    l.n_up = (int)(U * (E * F + S)); l.n_dn = (int)(E * F + S);
+    if (rg) { l.off_rg2 = l.n_up; l.n_up += (int)D; }   // the residual gate reads what the experts read: its rows follow theirs
     if (own) {
       XB_TRY(hy_alloc_t(hy, &l.w_up, (size_t)l.n_up * D));
       XB_TRY(hy_alloc_t(hy, &l.w_down, D * l.n_dn));
@@ -350,14 +389,20 @@ static int hy_create_ff(xb_engine* e, int i, bool own, uint64_t& wbytes) {
       hy_name_rows(hy, p + "router", l.w_router, 0, E, D);
       for (size_t x = 0; x < E; ++x) {
         const std::string pe = p + "e" + std::to_string(x) + ".";
-        hy_name_rows(hy, pe + "gate", l.w_up, 2 * x * F, F, D);
-        hy_name_rows(hy, pe + "up", l.w_up, 2 * x * F + F, F, D);
+        if (gated) hy_name_rows(hy, pe + "gate", l.w_up, 2 * x * F, F, D);
+        hy_name_rows(hy, pe + "up", l.w_up, gated ? 2 * x * F + F : x * F, F, D);
         hy_name_cols(hy, pe + "down", l.w_down, x * F, D, F, l.n_dn);
       }
       if (S > 0) {
-        hy_name_rows(hy, p + "shared.gate", l.w_up, 2 * E * F, S, D);
-        hy_name_rows(hy, p + "shared.up", l.w_up, 2 * E * F + S, S, D);
+        if (gated) hy_name_rows(hy, p + "shared.gate", l.w_up, 2 * E * F, S, D);
+        hy_name_rows(hy, p + "shared.up", l.w_up, gated ? 2 * E * F + S : E * F, S, D);
         hy_name_cols(hy, p + "shared.down", l.w_down, E * F, D, S, l.n_dn);
+      }
+      if (rg) {
+        const std::string pl = "l" + std::to_string(i) + ".";
+        XB_TRY(hy_alloc_t(hy, &l.b_up, (size_t)l.n_up));
+        hy_name_rows(hy, pl + "rg2", l.w_up, l.off_rg2, D, D);
+        hy_name_vec(hy, pl + "rg2.b", l.b_up + l.off_rg2, D);
       }
       wbytes += E * D * 2;
     }
@@ -389,8 +434,10 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
     const xb_hybrid_layer& c = l.d;
     const std::string p = "l" + std::to_string(i) + ".";
     const bool own = c.weights_of < 0;
-    const bool sandwich = d.block == XB_BLOCK_SANDWICH;
+    const bool sandwich = d.block == XB_BLOCK_SANDWICH, branchnorm = d.block == XB_BLOCK_BRANCHNORM;
     l.owner = -1;
+    XB_CHECK(!branchnorm || (own && (c.mixer == XB_MIX_SOFTMAX || c.mixer == XB_MIX_LATENT) && (c.ff == 0 || c.ff_kind == XB_FF_MOE)),
+             "layer %d: branch-norm blocks take softmax or latent attention and experts, with tensors of their own", i);
     if (!own) {
       XB_CHECK(c.weights_of < d.n_layers && c.weights_of != i && layers[c.weights_of].weights_of < 0,
                "layer %d: weights_of %d must name another layer that owns its tensors", i, c.weights_of);
@@ -488,10 +535,15 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
     } else {
       return xb_fail(1, "layer %d: unknown mixer kind %d", i, c.mixer);
     }
+    if (d.gated_residual && l.off_rg >= 0) {   // the mixer's residual gate: rows of the fused input projection
+      hy_name_rows(hy, p + "rg1", l.w_in, l.off_rg, D, D);
+      hy_name_vec(hy, p + "rg1.b", l.b_in + l.off_rg, D);
+    }
     if ((size_t)l.n_in > hy->maxN) hy->maxN = l.n_in;
     if ((size_t)l.n_o > hy->maxK) hy->maxK = l.n_o;
     if ((size_t)l.n_o2 > hy->maxK) hy->maxK = l.n_o2;
     if (c.ff > 0 && c.ff_kind != XB_FF_RELU2) {
+      if (branchnorm) { XB_TRY(hy_alloc_t(hy, &l.norm2, nd)); hy_name_vec(hy, p + "norm2", l.norm2, nd); }
       if (sandwich) {   // the feed-forward is a sublayer of its own: norm before and after, optionally the causal filter
         XB_CHECK(own && c.ff_kind == XB_FF_MOE, "layer %d: sandwich blocks take experts with tensors of their own", i);
         XB_TRY(hy_alloc_t(hy, &l.norm2, D)); hy_name_vec(hy, p + "norm2", l.norm2, D);
@@ -525,7 +577,18 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
       wbytes += 2 * sd * D * 2;
     }
   }
+  if (d.bigram_buckets > 0) { hy->st_prev = st; st += 1; }   // a slot's previous token
   hy->state_floats = st;
+  if (d.bigram_buckets > 0) {
+    XB_TRY(hy_alloc_t(hy, &hy->bigram, (size_t)(d.bigram_buckets + 1) * D));
+    hy_name_rows(hy, "bigram", hy->bigram, 0, d.bigram_buckets + 1, D);
+    wbytes += D * 2;
+  }
+  if (d.pos_rows > 0) {
+    XB_TRY(hy_alloc_t(hy, &hy->pos_tab, (size_t)d.pos_rows * D));
+    hy_name_rows(hy, "pos", hy->pos_tab, 0, d.pos_rows, D);
+    wbytes += D * 2;
+  }
   // layers that use another layer's tensors: the same device pointers, a cache and state of their own
   for (int i = 0; i < d.n_layers; ++i) {
     HyLayer& l = hy->L[i];
@@ -1103,26 +1166,67 @@ static int hy_latent_mma(xb_engine* e, const HyLayer& l, const BatchMeta& m, int
   return R <= 128 ? hy_latent_mma_launch<1, 128, 4>(e, l, m, T, ns, st) : hy_latent_mma_launch<1, 256, 4>(e, l, m, T, ns, st);
 }
 
+// Latent attention of one layer: P = [q | down-projection (| other rows)] of the step's rows -> a1 = what the output
+// projection reads.  The cache row is made and appended, the queries are folded into the cache's space, the attention
+// runs over the cached latents, and the read-out goes through the value up-projection.
+template <typename AT>
+static int hy_latent_mixer(xb_engine* e, const HyLayer& l, int T, const LinOut& P, const BatchMeta& m, cudaStream_t st) {
+  HyModel* hy = e->hy;
+  const xb_hybrid_layer& c = l.d;
+  const xb_hybrid_desc& d = hy->d;
+  typedef typename std::conditional<std::is_same<AT, float>::value, float, bf16>::type KT;
+  AT* a1 = reinterpret_cast<AT*>(hy->a1);
+  const int H = c.m_heads, n = c.m_dim;
+  const int dr = c.m_rot_dim, dv = c.m_vdim, R = c.m_kv_rank, W = R + dr;
+  XB_TRY(hy_launch(e, hy_latent_prep_kernel<KT>, dim3(T), dim3(256), 0, st, P, l.off_q, l.off_dkv, H, n, dr, R, c.m_rot_dims,
+                   (const float*)l.rot_freq, (const float*)l.lat_norm, d.norm_eps, (KT*)l.k_pool, m, hy->qa));
+  const size_t mm1 = (size_t)HY_MM_ROWS * n * sizeof(float), mm2 = (size_t)HY_MM_ROWS * R * sizeof(float);
+  XB_TRY(hy_launch(e, hy_head_mm_t_kernel, dim3((T + HY_MM_ROWS - 1) / HY_MM_ROWS, H), dim3(256), mm1, st, P, l.off_q, n + dr,
+                   (const bf16*)l.w_uk, hy->qa, (long long)H * W, W, T, n, R));
+  // bf16 serving at sizes the tensor-core tiles take: rows = (token, head) pairs over shared key tiles; steps of few
+  // rows split every sequence's keys over blocks and merge
+  bool done = false;
+  if (std::is_same<AT, bf16>::value && hy->use_lat_mma && W % 8 == 0 && R % 16 == 0) {
+    int rc = hy_latent_mma(e, l, m, T, st);
+    if (rc < 0) return -rc;
+    done = rc == 0;
+  }
+  if (!done) {
+    const int aw = 16;   // causal: every earlier key is visible
+    const size_t asm_bytes = (size_t)(((W + 3) & ~3) + aw * (2 + R)) * sizeof(float);
+    const LinOut Q = hy_plain(hy->qa, (long long)H * W);
+    const int far = 1 << 30;
+    if (R <= 256)
+      XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 8>, dim3(T, H), dim3(32 * aw), asm_bytes, st, Q, 0, -1, (const KT*)l.k_pool,
+                       (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R, AttnOpt{nullptr, 0.f, 1, 0}));
+    else
+      XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 16>, dim3(T, H), dim3(32 * aw), asm_bytes, st, Q, 0, -1, (const KT*)l.k_pool,
+                       (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R, AttnOpt{nullptr, 0.f, 1, 0}));
+  }
+  return hy_launch(e, hy_head_mm_kernel<AT>, dim3((T + HY_MM_ROWS - 1) / HY_MM_ROWS, H), dim3(128), mm2, st, (const float*)hy->o,
+                   (long long)H * R, (const bf16*)l.w_uv, a1, (long long)l.n_o, T, R, dv);
+}
+
 // ----------------------------------------------------------------------------- parallel blocks
 // x <- embed * scale;  per layer: h = norm(x) (made by the previous row op), x += mixer(h) + ff(h).
 // The mixers: latent attention (cache = latent + rotated key part, queries folded into the latent space so that a step
 // never rebuilds keys or values of earlier tokens), general delta rule, lightning; feed-forwards: clamped GLU, dense or experts.
 // xin: the normed stream as a Linear input [T, dim] of AT
 template <typename AT>
-static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, const void* xin, cudaStream_t st, LinOut* y) {
+static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, const void* xin, cudaStream_t st, LinOut* y, LinOut* up_out = nullptr) {
   HyModel* hy = e->hy;
   const xb_hybrid_layer& c = l.d;
   const int D = hy->d.dim;
   AT* a2 = reinterpret_cast<AT*>(hy->a2);
   // Steps of so few rows that at most half of the experts can have a token: read the chosen experts' rows only (two kernels
   // in place of the wide up Linear, the activation and the wide down Linear).
-  if (c.ff_kind == XB_FF_MOE && hy->use_gather && c.shared_ff <= 0 && l.b_up == nullptr && l.b_down == nullptr && D % 8 == 0 && c.ff % 8 == 0 &&
+  if (c.ff_kind == XB_FF_MOE && hy->use_gather && c.ff_act != XB_ACT_GELU && c.shared_ff <= 0 && l.b_up == nullptr && l.b_down == nullptr && D % 8 == 0 && c.ff % 8 == 0 &&
       2LL * T * c.top <= c.n_experts) {
     XB_TRY(hy_launch(e, hy_router_logits_kernel<AT, 1>, dim3((unsigned)(((long long)T * c.n_experts + 7) / 8)), dim3(256), 0, st,
                      reinterpret_cast<const AT*>(xin), (long long)D, (const bf16*)l.w_router, hy->m2, T, c.n_experts, D));
     const size_t rs = (size_t)4 * (2 * c.n_experts + (c.groups > 0 ? c.groups : 1)) * sizeof(float);
     XB_TRY(hy_launch(e, hy_route_kernel, dim3((T + 3) / 4), dim3(128), rs, st, hy_plain(hy->m2, c.n_experts), c.n_experts, c.top, c.groups,
-                     c.keep_groups, c.route_scale, hy->gw, T));
+                     c.keep_groups, c.route_scale, hy->gw, T, c.route_score, c.group_score, c.route_norm));
     const long long nu = (long long)T * c.top * c.ff, nd = (long long)T * D;
     XB_TRY(hy_launch(e, hy_moe_gather_up_kernel<AT>, dim3((unsigned)((nu + 7) / 8)), dim3(256), 0, st, reinterpret_cast<const AT*>(xin), (long long)D,
                      (const bf16*)l.w_up, (const float*)hy->gw, c.n_experts, c.top, c.ff, D, c.ff_limit, c.ff_act, c.route_input, a2, T));
@@ -1133,6 +1237,7 @@ static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, const void* xin
   }
   LinOut U;
   XB_TRY(hy_linear<AT>(e, xin, D, l.w_up, l.t_up, l.b_up, T, l.n_up, D, hy->P, hy->cap_P, st, &U));
+  if (up_out != nullptr) *up_out = U;   // rows behind the experts' (a residual gate) are read by the caller
   // a bf16 matrix out of the tcgen05 Linear (prompts): the activations read and write 16 bytes per thread
   const bool vec = std::is_same<AT, bf16>::value && U.h != nullptr && U.ld % 8 == 0 && l.n_dn % 8 == 0;
   if (c.ff_kind == XB_FF_GLU_CLAMP) {
@@ -1155,10 +1260,17 @@ static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, const void* xin
     const LinOut z = hy_plain(hy->m2, c.n_experts);
     const size_t rs = (size_t)4 * (2 * c.n_experts + (c.groups > 0 ? c.groups : 1)) * sizeof(float);
     XB_TRY(hy_launch(e, hy_route_kernel, dim3((T + 3) / 4), dim3(128), rs, st, z, c.n_experts, c.top, c.groups, c.keep_groups, c.route_scale,
-                     hy->gw, T));
+                     hy->gw, T, c.route_score, c.group_score, c.route_norm));
     const long long n = (long long)T * l.n_dn;
     const int sf = c.shared_ff > 0 ? c.shared_ff : 0;
-    if (vec && c.ff % 8 == 0 && sf % 8 == 0)
+    if (c.ff_act == XB_ACT_GELU) {   // experts without a gate projection
+      if (vec && c.ff % 8 == 0 && sf % 8 == 0)
+        XB_TRY(hy_launch(e, hy_moe_act1_vec_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, U.h, U.ld, (const float*)hy->gw, c.n_experts,
+                         c.ff, sf, reinterpret_cast<bf16*>(hy->a2), (long long)l.n_dn, T));
+      else
+        XB_TRY(hy_launch(e, hy_moe_act1_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, U, (const float*)hy->gw, c.n_experts, c.ff, sf,
+                         a2, (long long)l.n_dn, T));
+    } else if (vec && c.ff % 8 == 0 && sf % 8 == 0)
       XB_TRY(hy_launch(e, hy_moe_act_vec_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, U.h, U.ld, (const float*)hy->gw, c.n_experts,
                        c.ff, c.ff_limit, sf, c.shared_limit, c.ff_act, c.route_input, reinterpret_cast<bf16*>(hy->a2), (long long)l.n_dn, T));
     else
@@ -1203,34 +1315,7 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
     XB_TRY(hy_linear<AT>(e, hy->ah, D, l.w_in, l.t_in, l.b_in, T, l.n_in, D, hy->P, hy->cap_P, st, &P));
     const int H = c.m_heads, n = c.m_dim;
     if (c.mixer == XB_MIX_LATENT) {
-      const int dr = c.m_rot_dim, dv = c.m_vdim, R = c.m_kv_rank, W = R + dr;
-      XB_TRY(hy_launch(e, hy_latent_prep_kernel<KT>, dim3(T), dim3(256), 0, st, P, l.off_q, l.off_dkv, H, n, dr, R, c.m_rot_dims,
-                       (const float*)l.rot_freq, (const float*)l.lat_norm, d.norm_eps, (KT*)l.k_pool, m, hy->qa));
-      const size_t mm1 = (size_t)HY_MM_ROWS * n * sizeof(float), mm2 = (size_t)HY_MM_ROWS * R * sizeof(float);
-      XB_TRY(hy_launch(e, hy_head_mm_t_kernel, dim3((T + HY_MM_ROWS - 1) / HY_MM_ROWS, H), dim3(256), mm1, st, P, l.off_q, n + dr,
-                       (const bf16*)l.w_uk, hy->qa, (long long)H * W, W, T, n, R));
-      // bf16 serving at sizes the tensor-core tiles take: rows = (token, head) pairs over shared key tiles; steps of few
-      // rows split every sequence's keys over blocks and merge
-      if (std::is_same<AT, bf16>::value && hy->use_lat_mma && W % 8 == 0 && R % 16 == 0) {
-        int rc = hy_latent_mma(e, l, m, T, st);
-        if (rc < 0) return -rc;
-        if (rc == 0) goto latent_done;
-      }
-      {
-      const int aw = 16;   // causal: every earlier key is visible
-      const size_t asm_bytes = (size_t)(((W + 3) & ~3) + aw * (2 + R)) * sizeof(float);
-      const LinOut Q = hy_plain(hy->qa, (long long)H * W);
-      const int far = 1 << 30;
-      if (R <= 256)
-        XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 8>, dim3(T, H), dim3(32 * aw), asm_bytes, st, Q, 0, -1, (const KT*)l.k_pool,
-                         (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R, AttnOpt{nullptr, 0.f, 1, 0}));
-      else
-        XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 16>, dim3(T, H), dim3(32 * aw), asm_bytes, st, Q, 0, -1, (const KT*)l.k_pool,
-                         (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R, AttnOpt{nullptr, 0.f, 1, 0}));
-      }
-    latent_done:
-      XB_TRY(hy_launch(e, hy_head_mm_kernel<AT>, dim3((T + HY_MM_ROWS - 1) / HY_MM_ROWS, H), dim3(128), mm2, st, (const float*)hy->o,
-                       (long long)H * R, (const bf16*)l.w_uv, a1, (long long)l.n_o, T, R, dv));
+      XB_TRY(hy_latent_mixer<AT>(e, l, T, P, m, st));
     } else if (c.mixer == XB_MIX_GDELTA) {
       const int HN = H * n, rk = c.m_rank;
       LinOut Wd;
@@ -1313,7 +1398,11 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, i
   const int rope_by = T >= 512 ? 1 : (units + 255) / 256;
   const bool rope_vec = tc && P.h != nullptr && P.bias == nullptr && P.ld % 8 == 0 && dk % 8 == 0 && dv % 8 == 0 &&
                         c.s_rot_dims % (r.half ? 16 : 8) == 0 && (G * dv) % 8 == 0;
-  if (rope_vec)   // a prompt whose projection came back as a bf16 matrix: 16 bytes per thread
+  if (c.s_qk_norm != 0 || c.s_v_is_k != 0 || c.s_qtemp_every > 0)   // no rotation: whole-projection norms, temperature, append
+    XB_TRY(hy_launch(e, hy_qk_prep_kernel<KT>, dim3(T), dim3(256), (size_t)(H + G) * dk * sizeof(float), st, P, l.off_q, l.off_k, l.off_v, H, G, dk, dv,
+                     c.s_qk_norm ? (const float*)l.qn : (const float*)nullptr, c.s_qk_norm ? (const float*)l.kn : (const float*)nullptr, hy->d.norm_eps,
+                     c.s_qtemp_coef, c.s_qtemp_every, hy->qa, (tc || dec) ? hy->qg : (bf16*)nullptr, (KT*)l.k_pool, (KT*)l.v_pool, m));
+  else if (rope_vec)   // a prompt whose projection came back as a bf16 matrix: 16 bytes per thread
     XB_TRY(hy_launch(e, hy_rope_append_vec_kernel, dim3(T), dim3(256), 0, st, P.h, P.ld, l.off_q, l.off_k, l.off_v, H, G, dk, dv, r, hy->qg,
                      (bf16*)l.k_pool, (bf16*)l.v_pool, l.v_all ? 1 : 0, (const float*)l.vmix, hy->vfirst, l.vmode, m));
   else
@@ -1322,7 +1411,7 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, i
                    l.vmode, m));
   const int dvo = l.v_all ? G * dv : dv;
   const int vch = dvo > 512 ? 512 : 0;   // wider value rows: blocks along z take 512 channels each
-  const AttnOpt opt{c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : G, vch};
+  const AttnOpt opt{c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : G, vch, c.s_dist_bias ? l.r1 : nullptr, c.s_dist_bias ? l.r2 : nullptr};
   const bool post = c.s_talk != 0 || c.s_gate != 0;
   if (dec) {
     // mixed heads multiply the blocks by the key heads: fewer splits keep the grid near one wave
@@ -1371,11 +1460,80 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, i
   return 0;
 }
 
+// ----------------------------------------------------------------------------- branch-norm blocks
+// x <- embedding rows (token + token pair + position);  per layer  x += n1 unit(g1 * mixer(x)),  x += n2 unit(g2 * ff(x)),
+// g = sigmoid(W x + b) with the gate's rows riding in the sublayer's own input projection.  What a sublayer reads is the
+// stream itself (as a Linear input: xa, written by the kernel that last changed x); only the model's last norm exists as a row.
+template <typename AT>
+static int hy_run_branchnorm_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* const* taps, cudaStream_t st, int with_head) {
+  HyModel* hy = e->hy;
+  const xb_hybrid_desc& d = hy->d;
+  BatchMeta m;
+  fill_batch_meta(e, m);
+  m.page_table = e->d_page_table;
+  m.tile_start = e->d_tile_start;
+  m.tile_len = e->d_tile_len;
+  m.max_pages = e->max_pages;
+  m.page_tokens = e->page_tokens;
+  const int D = d.dim;
+  const long long SS = (long long)hy->state_floats;
+  hy->pdl_now = T <= 128;
+  AT* a1 = reinterpret_cast<AT*>(hy->a1);
+  const bool few = T <= 64 && D >= 1024;
+  auto row_op = [&](const LinOut& y, const LinOut& P, int off_gate, const float* bw, const float* nw) -> int {
+    RowOpArgs a;
+    a.x = hy->x; a.m1 = y; a.m2 = hy_none(); a.m3 = hy_none(); a.s1 = 1.f; a.s2 = 0.f; a.bw = bw; a.bw_one = 0.f; a.nw = nw; a.hn = hy->hn;
+    a.xa = a1; a.ha = nullptr; a.eps = d.norm_eps; a.D = D; a.plain_add = 0; a.nw_mode = d.norm_scalar ? 2 : 1; a.groups = 1; a.res_mult = 1.f; a.ext = 0;
+    a.gate = off_gate >= 0 ? P : hy_none(); a.gate_off = off_gate >= 0 ? off_gate : 0; a.bw_mode = d.norm_scalar ? 2 : 1;
+    if (few) return hy_launch(e, hy_row_op_gated_kernel<AT, 1024>, dim3(T), dim3(1024), (size_t)D * sizeof(float), st, a);
+    return hy_launch(e, hy_row_op_gated_kernel<AT, 256>, dim3(T), dim3(256), (size_t)D * sizeof(float), st, a);
+  };
+  const bool single = T == n_seqs;   // a step of single tokens: every row is its sequence's last
+  float* prev = hy->state + hy->st_prev;
+  XB_TRY(hy_launch(e, hy_embed_sum_kernel<AT>, dim3(T), dim3(128), 0, st, (const int*)e->in_tokens, (const bf16*)hy->embed, (const bf16*)hy->bigram,
+                   (const bf16*)hy->pos_tab, hy->x, a1, D, d.vocab, d.embed_scale, d.bigram_buckets, d.bigram_mul_prev, d.bigram_mul_cur, d.pos_rows,
+                   prev, SS, single ? 1 : 0, m));
+  if (hy->bigram != nullptr && !single)
+    XB_TRY(hy_launch(e, hy_prev_token_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, st, (const int*)e->in_tokens, prev, SS, d.vocab, n_seqs, m));
+  for (int li = 0; li < d.n_layers; ++li) {
+    const HyLayer& l = hy->L[li];
+    const xb_hybrid_layer& c = l.d;
+    const bool has_ff = c.ff > 0;
+    const bool last = li + 1 == d.n_layers;
+    LinOut P, y1;
+    XB_TRY(hy_linear<AT>(e, a1, D, l.w_in, l.t_in, l.b_in, T, l.n_in, D, hy->P, hy->cap_P, st, &P));
+    if (c.mixer == XB_MIX_LATENT) XB_TRY(hy_latent_mixer<AT>(e, l, T, P, m, st));
+    else XB_TRY(hy_softmax_mixer<AT>(e, l, T, n_seqs, n_tiles, P, m, st));
+    XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
+    XB_TRY(row_op(y1, P, l.off_rg, l.norm1, (last && !has_ff) ? hy->final_norm : nullptr));
+    if (has_ff) {
+      LinOut dn, U;
+      XB_TRY(hy_ff_parallel<AT>(e, l, T, a1, st, &dn, &U));
+      XB_TRY(row_op(dn, U, l.off_rg2, l.norm2, last ? hy->final_norm : nullptr));
+    }
+    if (taps != nullptr && taps[li] != nullptr)
+      XB_CUDA(cudaMemcpyAsync(taps[li], hy->x, (size_t)T * D * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  }
+  if (with_head) {
+    const int n = e->sel_rows != nullptr ? e->sel_n : n_seqs;
+    if (n > 0) {
+      const int* idx = e->sel_rows != nullptr ? hy->d_rows : m.seq_last;
+      LinOut y;
+      XB_TRY(hy_launch(e, hy_gather_rows_kernel<AT>, dim3(n), dim3(256), 0, st, (const float*)hy->hn, idx, reinterpret_cast<AT*>(hy->head_in), D));
+      XB_TRY(hy_linear<AT>(e, hy->head_in, D, hy->head, hy->t_head, nullptr, n, d.vocab, D, hy->head_raw, hy->cap_head, st, &y));
+      const long long tot = (long long)n * d.vocab;
+      XB_TRY(hy_launch(e, hy_logits_kernel, dim3((unsigned)((tot + 255) / 256)), dim3(256), 0, st, y, d.logit_softcap, e->logits, n, d.vocab));
+    }
+  }
+  return 0;
+}
+
 template <typename AT>
 static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* const* taps, cudaStream_t st, int with_head) {
   HyModel* hy = e->hy;
   const xb_hybrid_desc& d = hy->d;
   if (d.block == XB_BLOCK_PARALLEL) return hy_run_parallel_t<AT>(e, T, n_seqs, taps, st, with_head);
+  if (d.block == XB_BLOCK_BRANCHNORM) return hy_run_branchnorm_t<AT>(e, T, n_seqs, n_tiles, taps, st, with_head);
   typedef typename std::conditional<std::is_same<AT, float>::value, float, bf16>::type KT;
   BatchMeta m;
   fill_batch_meta(e, m);

@@ -89,6 +89,60 @@ __global__ void hy_embed_kernel(const int* __restrict__ tokens, const bf16* __re
   for (int i = threadIdx.x; i < D; i += blockDim.x) x[(long long)t * D + i] = bf2f(emb[(long long)tok * D + i]) * scale;
 }
 
+// Embedding as a sum of three rows: the token's, a hashed row of the (previous token, token) pair and a learned position row.
+//   x[t] = emb[tok] * scale + bigram[(prev * mul_prev + tok * mul_cur) mod buckets] + pos_tab[position]
+// A sequence's first token (position 0) takes row `buckets` of the pair table.  The previous token of a row that opens a
+// step's portion comes from the slot's state (prev_state[slot * SS], the token's bits in a float), written by the step that
+// ran the token before it.  write_prev: a step of single tokens, where the row is also its sequence's last, stores its own
+// token there; other steps launch hy_prev_token_kernel behind this kernel (a block of another row may still read the word).
+// xa: the row as a Linear input.  bigram / pos_tab may be nullptr (that term is absent).
+template <typename AT>
+__global__ void hy_embed_sum_kernel(const int* __restrict__ tokens, const bf16* __restrict__ emb, const bf16* __restrict__ bigram,
+                                    const bf16* __restrict__ pos_tab, float* __restrict__ x, AT* __restrict__ xa, int D, int V, float scale,
+                                    int buckets, int mul_prev, int mul_cur, int pos_rows, float* __restrict__ prev_state, long long SS,
+                                    int write_prev, BatchMeta m) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+  const int s = m.tok_seq[t], pos = m.tok_pos[t];
+  const bf16* brow = nullptr;
+  if (bigram != nullptr) {
+    long long row = buckets;
+    if (pos > 0) {
+      int prev;
+      if (t > 0 && m.tok_seq[t - 1] == s) prev = tokens[t - 1];
+      else prev = __float_as_int(prev_state[(long long)m.seq_slot[s] * SS]);
+      prev = prev < 0 ? 0 : (prev >= V ? V - 1 : prev);
+      row = ((long long)prev * mul_prev + (long long)tok * mul_cur) % buckets;
+    }
+    brow = bigram + row * D;
+  }
+  const bf16* prow = pos_tab != nullptr ? pos_tab + (long long)(pos < pos_rows ? pos : pos_rows - 1) * D : nullptr;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float v = bf2f(emb[(long long)tok * D + i]) * scale;
+    if (brow != nullptr) v += bf2f(brow[i]);
+    if (prow != nullptr) v += bf2f(prow[i]);
+    x[(long long)t * D + i] = v;
+    if (xa != nullptr) act_store<AT>(xa + (long long)t * D + i, v);
+  }
+  if (write_prev && bigram != nullptr) {
+    __syncthreads();   // every thread of the row has read the old word (only thread-uniform reads above, but keep the order plain)
+    if (threadIdx.x == 0) prev_state[(long long)m.seq_slot[s] * SS] = __int_as_float(tok);
+  }
+}
+// the last token of every sequence of the step becomes its slot's "previous token"
+__global__ void hy_prev_token_kernel(const int* __restrict__ tokens, float* __restrict__ prev_state, long long SS, int V, int n_seqs, BatchMeta m) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= n_seqs) return;
+  int tok = tokens[m.seq_last[s]];
+  tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+  prev_state[(long long)m.seq_slot[s] * SS] = __int_as_float(tok);
+}
+
 // ----------------------------------------------------------------------------- residual + norms, one block per row
 // m   = s1 * m1 + s2 * m2                         (branch output; absent when m1 has no data)
 // x  += m / rms(m) * (bw + bw_one)                (bw_one = 1: weight stored as an offset from one; 0: plain weight)
@@ -114,6 +168,10 @@ struct RowOpArgs {
   int groups;       // > 1: every norm divides each of `groups` equal consecutive parts of the row by its own root mean square
   float res_mult;   // the normed branch is multiplied by this before it joins the stream
   int ext;          // the sandwich wrapper sets it when a model uses any of: groups, res_mult, plain weights, ha
+  // read by hy_row_op_gated_kernel only:
+  LinOut gate;      // the branch is multiplied by sigmoid(gate[t, gate_off + i]) before its norm; no data = no gate
+  int gate_off;
+  int bw_mode;      // branch-norm weight: 1 = plain weight bw[i]; 2 = one number bw[0]
 };
 #define HY_MAX_NORM_GROUPS 64
 // 1 / sqrt(mean(part^2) + eps) of each part of row[0, D) into ginv: a warp per part, lanes stride the part (a fixed order,
@@ -273,6 +331,44 @@ __device__ __forceinline__ void hy_st8f(float* p, const float* v) {
   *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
   *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
 }
+// Branch-norm blocks: the sublayer read the stream itself, only its output is normed.
+//   y   = m1 * sigmoid(gate)                       (gate optional)
+//   x  += y / rms(y) * weight(bw)                  (bw_mode: a weight per channel or one number)
+//   xa  = x as a Linear input (what the next sublayer reads);  hn = x / rms(x) * weight(nw)  (the model's last norm; nw may be nullptr)
+// All of it in fp32; one block per row, the row in shared memory.
+template <typename AT, int NT>
+__global__ void __launch_bounds__(NT) hy_row_op_gated_kernel(RowOpArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  const int D = a.D;
+  float* x = a.x + t * D;
+  const bool gated = a.gate.f != nullptr || a.gate.h != nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += NT) {
+    float v = lin_at(a.m1, t, i);
+    if (gated) v *= hy_sigmoid(lin_at(a.gate, t, a.gate_off + i));
+    row[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum<NT>(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
+  float s2 = 0.f;
+  for (int i = threadIdx.x; i < D; i += NT) {
+    const float v = x[i] + row[i] * inv * (a.bw_mode == 2 ? a.bw[0] : a.bw[i]);
+    x[i] = v;
+    row[i] = v;
+    s2 = fmaf(v, v, s2);
+    if (a.xa != nullptr) act_store<AT>(reinterpret_cast<AT*>(a.xa) + t * D + i, v);
+  }
+  if (a.nw == nullptr) return;
+  s2 = block_sum<NT>(s2, red);
+  const float inv2 = 1.0f / sqrtf(s2 / (float)D + a.eps);
+  for (int i = threadIdx.x; i < D; i += NT) a.hn[t * D + i] = row[i] * inv2 * hy_norm_weight(a.nw, a.nw_mode, i);
+}
+
 template <typename AT> __device__ __forceinline__ void hy_st8a(AT* p, const float* v);
 template <> __device__ __forceinline__ void hy_st8a<float>(float* p, const float* v) { hy_st8f(p, v); }
 template <> __device__ __forceinline__ void hy_st8a<bf16>(bf16* p, const float* v) {
@@ -1000,11 +1096,14 @@ __global__ void hy_qg_pack_kernel(LinOut P, int off_q, int nq, int off_g, int ng
 // ([page][token][G * dv], dv here = that whole width), so that one query head's weights meet all of them.
 // v_chunk > 0: block z handles value channels [z * v_chunk, (z + 1) * v_chunk) of the row (rows wider than the 512 channels a
 // block's lanes can carry; every block recomputes the scores).
+// r1 / r2 (per head, both or neither): r1[h] * ln(1 + r2[h] * (query position - key position)) is taken off the scaled score.
 struct AttnOpt {
   const float* sink;
   float softcap;
   int v_heads;
   int v_chunk;
+  const float* r1;
+  const float* r2;
 };
 template <typename KT, typename AT, int NACC>
 __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q, int off_gate, const KT* __restrict__ k_pool,
@@ -1052,6 +1151,7 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
       prow = opt.v_heads == G ? krow : pg * m.page_tokens + ip;   // the value row (shared with the other lanes below)
       sc = (ldk & 7) == 0 ? hy_dot_row<KT>(q, k_pool + krow * ldk, dk) : hy_dot_row_any<KT>(q, k_pool + krow * ldk, dk);
       if (opt.softcap > 0.f) sc = opt.softcap * tanhf(sc / opt.softcap);
+      if (opt.r1 != nullptr) sc -= opt.r1[h] * log1pf(opt.r2[h] * (float)(pos - kp));
     }
     const float tmax = warp_max(sc);
     const float nm = fmaxf(mx, tmax);
@@ -1145,6 +1245,55 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
       if (off_gate >= 0) v *= hy_sigmoid(lin_at(P, row, off_gate + h * dv_full + voff + d));
       act_store<AT>(out + (long long)row * ld_out + (long long)h * dv_full + voff + d, v);
     }
+  }
+}
+
+// ----------------------------------------------------------------------------- whole-projection q / k norms, query temperature, cache append
+// Attention without rotation whose queries and keys are RMS-normed over the WHOLE projection (all heads of a token as one
+// vector, a weight per channel; qn / kn nullptr = no norm) and whose queries carry a temperature that grows with the
+// position, q *= 1 + coef * ln(floor((pos + 1) / every) + 1) (every = 0: none).  One block per token, the token's q and k
+// channels in shared memory ((H + G) * dk floats):
+//   qa[t]  (fp32, rows of H * dk)  and, when asked, qg[t] (bf16, for a tensor-core kernel) = the finished queries
+//   k_pool [page][G][token][dk]    = the finished keys
+//   v_pool [page][G][token][dv]    = P[t, off_v ...]: the value projection, or with off_v = off_k (dv = dk) the keys as they were
+//                                    projected, before the norm
+// Everything after the projection is fp32.
+template <typename KT>
+__global__ void __launch_bounds__(256) hy_qk_prep_kernel(LinOut P, int off_q, int off_k, int off_v, int H, int G, int dk, int dv,
+                                                         const float* __restrict__ qn, const float* __restrict__ kn, float eps,
+                                                         float temp_coef, int temp_every, float* __restrict__ qa, bf16* __restrict__ qg,
+                                                         KT* __restrict__ k_pool, KT* __restrict__ v_pool, BatchMeta m) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float qk[];
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int nq = H * dk, nk = G * dk, nv = G * dv;
+  const int s = m.tok_seq[row], pos = m.tok_pos[row];
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < nq; i += 256) { const float v = lin_at(P, row, off_q + i); qk[i] = v; sq = fmaf(v, v, sq); }
+  for (int i = threadIdx.x; i < nk; i += 256) { const float v = lin_at(P, row, off_k + i); qk[nq + i] = v; sk = fmaf(v, v, sk); }
+  float qs = 1.f, ks = 1.f;
+  if (qn != nullptr) qs = 1.0f / sqrtf(block_sum<256>(sq, red) / (float)nq + eps);
+  if (kn != nullptr) ks = 1.0f / sqrtf(block_sum<256>(sk, red) / (float)nk + eps);
+  __syncthreads();
+  const float temp = temp_every > 0 ? 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f) : 1.0f;
+  for (int i = threadIdx.x; i < nq; i += 256) {
+    const float v = qn != nullptr ? qk[i] * qs * qn[i] * temp : qk[i] * temp;
+    qa[(long long)row * nq + i] = v;
+    if (qg != nullptr) qg[(long long)row * nq + i] = f2bf(v);
+  }
+  const long long pg = m.page_table[(long long)m.seq_slot[s] * m.max_pages + pos / m.page_tokens];
+  const int ip = pos % m.page_tokens;
+  for (int i = threadIdx.x; i < nk; i += 256) {
+    const int g = i / dk, c = i - g * dk;
+    const float v = kn != nullptr ? qk[nq + i] * ks * kn[i] : qk[nq + i];
+    act_store<KT>(k_pool + ((pg * G + g) * m.page_tokens + ip) * dk + c, v);
+  }
+  for (int i = threadIdx.x; i < nv; i += 256) {
+    const int g = i / dv, c = i - g * dv;
+    const float v = off_v == off_k ? qk[nq + i] : lin_at(P, row, off_v + i);
+    act_store<KT>(v_pool + ((pg * G + g) * m.page_tokens + ip) * dv + c, v);
   }
 }
 
@@ -1842,7 +1991,11 @@ __global__ void __launch_bounds__(256) hy_router_logits_kernel(const AT* __restr
 // two best scores and only experts of the `keep` best groups are eligible; the `top` best eligible experts get
 // score * scale (no renormalisation).  Ties go to the lower index.  One warp per token; shared memory 2 * E + groups floats
 // per warp.
-__global__ void __launch_bounds__(128) hy_route_kernel(LinOut z, int E, int top, int groups, int keep, float scale, float* __restrict__ gw, int T) {
+// score_mode: XB_ROUTE_SIGMOID, or XB_ROUTE_SOFTMAX = softmax of the logits over all experts.  group_mode: XB_GROUP_TOP2 as above,
+// or XB_GROUP_MAX = a group is worth its best score.  renorm: the chosen experts' scores are divided by their sum (+ 1e-20)
+// before the scale.
+__global__ void __launch_bounds__(128) hy_route_kernel(LinOut z, int E, int top, int groups, int keep, float scale, float* __restrict__ gw, int T,
+                                                       int score_mode, int group_mode, int renorm) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float rsm[];
@@ -1852,10 +2005,20 @@ __global__ void __launch_bounds__(128) hy_route_kernel(LinOut z, int E, int top,
   float* sc = rsm + (size_t)warp * (2 * E + (groups > 0 ? groups : 1));
   float* el = sc + E;      // eligible score, or -1 once taken / not eligible
   float* gs = el + E;
-  for (int e = lane; e < E; e += 32) {
-    const float v = hy_sigmoid(lin_at(z, t, e));
-    sc[e] = v;
-    el[e] = v;
+  if (score_mode == XB_ROUTE_SOFTMAX) {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) { const float v = lin_at(z, t, e); sc[e] = v; mx = fmaxf(mx, v); }
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float v = expf(sc[e] - mx); sc[e] = v; sum += v; }
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) { const float v = sc[e] / sum; sc[e] = v; el[e] = v; }
+  } else {
+    for (int e = lane; e < E; e += 32) {
+      const float v = hy_sigmoid(lin_at(z, t, e));
+      sc[e] = v;
+      el[e] = v;
+    }
   }
   __syncwarp();
   if (groups > 0 && keep < groups) {
@@ -1866,7 +2029,7 @@ __global__ void __launch_bounds__(128) hy_route_kernel(LinOut z, int E, int top,
         const float v = sc[g * per + i];
         if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) b2 = v;
       }
-      gs[g] = b1 + (per > 1 ? b2 : 0.f);
+      gs[g] = group_mode == XB_GROUP_MAX ? b1 : b1 + (per > 1 ? b2 : 0.f);
     }
     __syncwarp();
     // a group stays when fewer than `keep` groups beat it (a tie counts for the lower index)
@@ -1879,6 +2042,7 @@ __global__ void __launch_bounds__(128) hy_route_kernel(LinOut z, int E, int top,
     __syncwarp();
   }
   for (int e = lane; e < E; e += 32) gw[t * E + e] = 0.f;
+  float tot = 0.f;   // sum of the chosen scores (every lane follows the same picks)
   for (int r = 0; r < top; ++r) {
     float bv = -1.f;
     int bi = E;
@@ -1891,8 +2055,14 @@ __global__ void __launch_bounds__(128) hy_route_kernel(LinOut z, int E, int top,
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
     if (bi >= E || bv < 0.f) break;
+    tot += bv;
     if (lane == 0) { gw[t * E + bi] = sc[bi] * scale; el[bi] = -1.f; }
     __syncwarp();
+  }
+  if (renorm) {
+    const float inv = 1.0f / (tot + 1e-20f);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) gw[t * E + e] *= inv;   // the entries of experts that were not chosen are zero
   }
 }
 
@@ -1919,6 +2089,50 @@ __global__ void hy_moe_act_kernel(LinOut U, const float* __restrict__ gw, int E,
     v = hy_expert_act(lin_at(U, t, 2 * E * f + j), lin_at(U, t, 2 * E * f + sf + j), 1.0f, limit_s, act, 0);
   }
   act_store<AT>(out + t * ld_out + i, v);
+}
+
+// Experts without a gate projection (XB_ACT_GELU): U carries every expert's up rows [up_e (f)], then the shared expert's (sf).
+// out[t, e * f + i] = gw[t, e] * gelu(up) (zero for experts the token does not use), out[t, E * f + i] = gelu(up) of the shared
+// expert: the input of ONE down projection over all experts' columns.  gelu is the exact form, 0.5 z (1 + erf(z / sqrt 2)).
+__device__ __forceinline__ float hy_gelu_erf(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f)); }
+template <typename AT>
+__global__ void hy_moe_act1_kernel(LinOut U, const float* __restrict__ gw, int E, int f, int sf, AT* __restrict__ out, long long ld_out, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int W = E * f + sf;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)T * W) return;
+  const long long t = idx / W;
+  const int i = (int)(idx - t * W);
+  float v = 0.f;
+  if (i < E * f) {
+    const float g = gw[t * E + i / f];
+    if (g != 0.f) v = g * hy_gelu_erf(lin_at(U, t, i));
+  } else {
+    v = hy_gelu_erf(lin_at(U, t, i));
+  }
+  act_store<AT>(out + t * ld_out + i, v);
+}
+// the same on a bf16 matrix (prompts), eight neighbours per thread: f, sf, ld, ld_out multiples of 8
+__global__ void hy_moe_act1_vec_kernel(const bf16* __restrict__ u, long long ld, const float* __restrict__ gw, int E, int f, int sf,
+                                       bf16* __restrict__ out, long long ld_out, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int W8 = (E * f + sf) >> 3;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)T * W8) return;
+  const long long t = idx / W8;
+  const int i = (int)(idx - t * W8) << 3;
+  const float w = i < E * f ? gw[t * E + i / f] : 1.0f;
+  uint4 r = make_uint4(0u, 0u, 0u, 0u);
+  if (w != 0.f) {
+    float v[8];
+    hy_load8(u + t * ld + i, nullptr, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = w * hy_gelu_erf(v[j]);
+    r = make_uint4(f2_to_bf2(v[0], v[1]), f2_to_bf2(v[2], v[3]), f2_to_bf2(v[4], v[5]), f2_to_bf2(v[6], v[7]));
+  }
+  *reinterpret_cast<uint4*>(out + t * ld_out + i) = r;
 }
 
 // Experts gathered: steps of so few rows that most experts have no token read only the rows of the chosen experts instead of

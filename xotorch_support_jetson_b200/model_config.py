@@ -28,7 +28,7 @@ _DIRECT_FIELDS = (
 _OPTIONAL_FIELDS = (("attention_dropout", "attn_dropout", 0.0), ("attention_bias", "attn_bias", False), ("hidden_act", "hidden_act", "silu"))
 
 
-HYBRID_ARCHITECTURES = ("Refatar", "Bibevik", "Pufivik")
+HYBRID_ARCHITECTURES = ("Refatar", "Bibevik", "Pufivik", "Vusenex")
 
 
 def is_hybrid(config: dict) -> bool:
@@ -52,6 +52,8 @@ def hybrid_model_config(raw: dict) -> dict:
     return bibevik_model_config(raw)
   if arch == "Pufivik":
     return pufivik_model_config(raw)
+  if arch == "Vusenex":
+    return vusenex_model_config(raw)
   layers = []
   for i, lc in enumerate(raw["layers"]):
     mx, kind = lc["mixer"], lc["type"]
@@ -191,6 +193,60 @@ def pufivik_model_config(raw: dict) -> dict:
     "embed_dim": int(raw["width"]), "vocab_size": int(raw["vocab"]), "num_layers": len(layers),
     "max_seq_len": int(raw.get("max_seq_len", 1 << 20)), "norm_eps": float(norm["eps"]),
     "taps": int(canon["taps"]) if canon else 0, "side_dim": 0, "logit_softcap": 0.0, "layers": layers,
+    "torch_dtype": HF_PRECISION_STR_TO_DTYPE.get(raw.get("torch_dtype", "bfloat16"), torch.bfloat16),
+  }
+
+
+def vusenex_model_config(raw: dict) -> dict:
+  """A Vusenex ``config.json`` (``width``, ``vocab``, ``max_positions``, ``embedding.bigram`` {buckets, mul_prev, mul_cur},
+  ``norm.eps``, ``layers`` [{type, mixer, mlp}]) -> the engine's dict.  Layers are branch-norm blocks: a sublayer reads the
+  stream itself, its output is gated by a sigmoid of the stream, RMS-normed with a single number and added.  The embedding is
+  the token row plus a hashed row of the (previous, current) token pair plus a learned position row.  Mixer kinds:
+  ``attention`` {heads, kv_heads, dim, vdim, scale, q_temp{coef, every}} = grouped-query softmax attention without rotation
+  whose values are the projected keys, with q / k biases, whole-projection q / k norms, a query temperature, a logarithmic
+  distance penalty per head and one extra unit in the softmax denominator; ``latent_attention`` {heads, dim, vdim, kv_rank,
+  scale} = attention over a cached latent without a rotated part.  ``mlp``: null or experts {expert{ff}, router{experts, top,
+  groups{count, keep}}, shared{ff}} of the ungated erf-GELU form with softmax scores, groups worth their best score and
+  weights renormalised over the chosen experts."""
+  layers = []
+  for i, lc in enumerate(raw["layers"]):
+    mx, kind = lc["mixer"], lc["type"]
+    if kind == "attention":
+      if int(mx.get("vdim", mx["dim"])) != int(mx["dim"]):
+        raise ValueError(f"layer {i}: values are the projected keys, so vdim {mx['vdim']} must equal dim {mx['dim']}")
+      qt = mx.get("q_temp") or {}
+      lay = {"mixer": "softmax", "heads": int(mx["heads"]), "kv_heads": int(mx["kv_heads"]), "dim": int(mx["dim"]), "vdim": int(mx["dim"]),
+             "scale": float(mx["scale"]), "softcap": 0.0, "sink": "unit", "talk": False, "gate": False, "v_mix": False,
+             "qkv_bias": True, "qk_norm": True, "v_is_k": True, "dist_bias": True,
+             "qtemp_coef": float(qt.get("coef", 0.0)), "qtemp_every": int(qt.get("every", 0))}
+      lay.update(_rotary(i, None, kind))
+    elif kind == "latent_attention":
+      lay = {"mixer": "latent", "heads": int(mx["heads"]), "dim": int(mx["dim"]), "rot_dim": 0, "vdim": int(mx["vdim"]),
+             "kv_rank": int(mx["kv_rank"]), "scale": float(mx["scale"]), "rot_base": 10000.0, "rot_dims": 0}
+    else:
+      raise ValueError(f"layer {i}: unknown layer type {kind!r}")
+    mlp = lc.get("mlp")
+    if mlp is None:
+      lay.update({"ff": 0, "ff_kind": "none"})
+    elif mlp.get("kind", "moe") == "moe":
+      rt, sh = mlp["router"], mlp.get("shared")
+      gr = rt.get("groups")
+      lay.update({"ff": int(mlp["expert"]["ff"]), "ff_kind": "moe", "ff_act": "gelu", "route_input": False, "ff_limit": 0.0,
+                  "experts": int(rt["experts"]), "top": int(rt["top"]), "groups": int(gr["count"]) if gr else 0,
+                  "keep_groups": int(gr["keep"]) if gr else 0, "route_scale": 1.0, "route_score": "softmax", "group_score": "max",
+                  "route_norm": True, "shared_ff": int(sh["ff"]) if sh else 0, "shared_limit": 0.0})
+    else:
+      raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+    lay["weights_of"] = -1
+    layers.append(lay)
+  bg = (raw.get("embedding") or {}).get("bigram")
+  return {
+    "family": "hybrid", "architecture": "Vusenex", "block": "branchnorm", "norm_scalar": True, "gated_residual": True,
+    "bigram": {"buckets": int(bg["buckets"]), "mul_prev": int(bg["mul_prev"]), "mul_cur": int(bg["mul_cur"])} if bg else None,
+    "pos_rows": int(raw["max_positions"]), "embed_scale": 1.0,
+    "embed_dim": int(raw["width"]), "vocab_size": int(raw["vocab"]), "num_layers": len(layers),
+    "max_seq_len": int(raw["max_positions"]), "norm_eps": float(raw["norm"]["eps"]),
+    "taps": 0, "side_dim": 0, "logit_softcap": 0.0, "layers": layers,
     "torch_dtype": HF_PRECISION_STR_TO_DTYPE.get(raw.get("torch_dtype", "bfloat16"), torch.bfloat16),
   }
 

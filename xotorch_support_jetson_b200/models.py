@@ -161,6 +161,41 @@ _PUFIVIK_1B = _pufivik(2048, 128256, [
   (("attention", _sink_attn(32, 8, 64, 64, 32), _swiglu_experts(8, 2, 1024)) if i % 4 == 1 else
    ("attention_2", _cap_attn(32, 8, 64, 64, 64), _swiglu_experts(8, 2, 1024))) for i in range(16)], scale=45.0)
 
+def _vusenex(width, vocab, layers, max_pos=4096, buckets=4093, mul_prev=37, mul_cur=11, eps=1e-6):
+  """A Vusenex config.json: layers is a list of (type, mixer, mlp) entries."""
+  return {"architecture": "Vusenex", "width": width, "vocab": vocab, "max_positions": max_pos,
+          "embedding": {"bigram": {"buckets": buckets, "mul_prev": mul_prev, "mul_cur": mul_cur}}, "norm": {"eps": eps},
+          "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in layers]}
+
+
+def _kv_attn(heads, kv, dim, coef=0.2, every=64):
+  return {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "q_temp": {"coef": coef, "every": every}}
+
+
+def _plain_latent(heads, dim, vdim, rank):
+  return {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": rank, "scale": dim ** -0.5}
+
+
+def _gelu_experts(n, top, ff, groups, keep, shared_ff):
+  m = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": n, "top": top, "groups": {"count": groups, "keep": keep}}}
+  if shared_ff:
+    m["shared"] = {"ff": shared_ff}
+  return m
+
+
+_VUSENEX_TINY = _vusenex(160, 448, [
+  ("latent_attention", _plain_latent(5, 24, 40, 48), _gelu_experts(8, 2, 48, 4, 2, 64)),
+  ("attention", _kv_attn(6, 3, 40), _gelu_experts(6, 3, 32, 3, 2, 0)),
+  ("attention", _kv_attn(4, 1, 24, coef=0.5, every=16), None),
+  ("latent_attention", _plain_latent(3, 32, 32, 80), _gelu_experts(8, 2, 48, 4, 2, 64)),
+], max_pos=1024, buckets=509)
+# 1B-class geometry for throughput runs (random weights): the widths of llama-3.2-1b (32 query / 8 key heads of 64), latent
+# layers of 16 heads over a latent of 256, 16 experts of 512 of which a token uses four (the width of four of them plus the
+# shared expert = half of Llama's feed-forward)
+_VUSENEX_1B = _vusenex(2048, 128256, [
+  (("attention", _kv_attn(32, 8, 64, coef=0.3, every=128), _gelu_experts(16, 4, 512, 4, 3, 2048)) if i % 4 in (0, 3) else
+   ("latent_attention", _plain_latent(16, 64, 128, 256), _gelu_experts(16, 4, 512, 4, 3, 2048))) for i in range(16)], max_pos=8192, buckets=65521)
+
 # model id -> {layers, repo:{EngineClassName: hf repo}, hf_config}
 model_cards = {
   "llama-3.2-1b": {"layers": 16, "repo": {ENGINE_CLASS_NAME: "unsloth/Llama-3.2-1B-Instruct"},
@@ -186,6 +221,8 @@ model_cards = {
   "bibevik-1b": {"layers": 16, "repo": {ENGINE_CLASS_NAME: "synthetic/bibevik-1b"}, "hf_config": _BIBEVIK_1B},
   "pufivik-tiny": {"layers": 4, "repo": {ENGINE_CLASS_NAME: "synthetic/pufivik-tiny"}, "hf_config": _PUFIVIK_TINY},
   "pufivik-1b": {"layers": 16, "repo": {ENGINE_CLASS_NAME: "synthetic/pufivik-1b"}, "hf_config": _PUFIVIK_1B},
+  "vusenex-tiny": {"layers": 4, "repo": {ENGINE_CLASS_NAME: "synthetic/vusenex-tiny"}, "hf_config": _VUSENEX_TINY},
+  "vusenex-1b": {"layers": 16, "repo": {ENGINE_CLASS_NAME: "synthetic/vusenex-1b"}, "hf_config": _VUSENEX_1B},
   "mistral-tiny": {"layers": 4, "repo": {ENGINE_CLASS_NAME: "synthetic/mistral-tiny"},
                    "hf_config": _mistral(320, 5, 1, 640, 4, head_dim=64, vocab=1280)},
 }

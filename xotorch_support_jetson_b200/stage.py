@@ -121,6 +121,9 @@ class StageRuntime:
       raise ValueError("a hybrid model runs as one full-model stage (its fp32 residual stream has no hand-off format)")
     self.family, self.tied, self.qkv_bias = "hybrid", False, False
     self.compute_dtype = dtype
+    if config.get("pos_rows"):   # a learned position table bounds the sequence length
+      max_tokens_per_seq = min(max_tokens_per_seq, int(config["pos_rows"]))
+    bg = config.get("bigram")
     self.max_seqs, self.max_batch_tokens, self.max_tokens_per_seq = max_seqs, max_batch_tokens, max_tokens_per_seq
     self.max_positions = max_tokens_per_seq
     self.max_logit_rows = int(max_logit_rows if max_logit_rows is not None else max_seqs)
@@ -134,13 +137,19 @@ class StageRuntime:
       if lc.get("ff_kind") == "moe":
         L.n_experts, L.top, L.groups, L.keep_groups = lc["experts"], lc["top"], lc["groups"], lc["keep_groups"]
         L.route_scale, L.shared_ff, L.shared_limit = lc["route_scale"], lc["shared_ff"], lc["shared_limit"]
-        L.ff_act = {"glu_clamp": _cabi.ACT_GLU_CLAMP, "swiglu": _cabi.ACT_SWIGLU}[lc.get("ff_act", "glu_clamp")]
+        L.ff_act = {"glu_clamp": _cabi.ACT_GLU_CLAMP, "swiglu": _cabi.ACT_SWIGLU, "gelu": _cabi.ACT_GELU}[lc.get("ff_act", "glu_clamp")]
         L.route_input = int(bool(lc.get("route_input", False)))
+        L.route_score = {"sigmoid": _cabi.ROUTE_SIGMOID, "softmax": _cabi.ROUTE_SOFTMAX}[lc.get("route_score", "sigmoid")]
+        L.group_score = {"top2": _cabi.GROUP_TOP2, "max": _cabi.GROUP_MAX}[lc.get("group_score", "top2")]
+        L.route_norm = int(bool(lc.get("route_norm", False)))
       if lc["mixer"] == "softmax":
         L.mixer = _cabi.MIX_SOFTMAX
         L.s_heads, L.s_kv_heads, L.s_dim, L.s_vdim = lc["heads"], lc["kv_heads"], lc["dim"], lc["vdim"]
         L.s_scale, L.s_softcap = lc["scale"], lc.get("softcap", 0.0)
-        L.s_sink, L.s_talk, L.s_gate, L.s_vmix = (int(bool(lc.get(k))) for k in ("sink", "talk", "gate", "v_mix"))
+        L.s_talk, L.s_gate, L.s_vmix = (int(bool(lc.get(k))) for k in ("talk", "gate", "v_mix"))
+        L.s_sink = _cabi.SINK_UNIT if lc.get("sink") == "unit" else int(bool(lc.get("sink")))
+        L.s_qkv_bias, L.s_qk_norm, L.s_v_is_k, L.s_dist_bias = (int(bool(lc.get(k))) for k in ("qkv_bias", "qk_norm", "v_is_k", "dist_bias"))
+        L.s_qtemp_coef, L.s_qtemp_every = lc.get("qtemp_coef", 0.0), lc.get("qtemp_every", 0)
         L.s_rot_dims = lc.get("rot_dims", 0)
         L.s_rot_pairs = _cabi.ROPE_HALF_SPLIT if lc.get("rot_pairs", "half") == "half" else _cabi.ROPE_INTERLEAVED
         L.s_rot_scaling = {"none": _cabi.ROT_SCALE_NONE, "bands": _cabi.ROT_SCALE_BANDS, "ramp": _cabi.ROT_SCALE_RAMP}[lc.get("rot_scaling", "none")]
@@ -173,11 +182,14 @@ class StageRuntime:
       n_layers=nl, dim=config["embed_dim"], vocab=config["vocab_size"], taps=config["taps"], side_dim=config["side_dim"],
       norm_eps=config["norm_eps"], logit_softcap=config["logit_softcap"], compute_fp32=int(dtype == "float32"),
       max_batch_tokens=max_batch_tokens, max_seqs=max_seqs, max_logit_rows=self.max_logit_rows,
-      block=_cabi.BLOCK_PARALLEL if config.get("block") == "parallel" else _cabi.BLOCK_SANDWICH,
+      block={"parallel": _cabi.BLOCK_PARALLEL, "branchnorm": _cabi.BLOCK_BRANCHNORM}.get(config.get("block"), _cabi.BLOCK_SANDWICH),
       norm_scalar=int(bool(config.get("norm_scalar", False))), embed_scale=float(config.get("embed_scale", 1.0)),
       norm_groups=int(config.get("norm_groups", 1)), norm_plain=int(bool(config.get("norm_plain", False))),
       residual_mult=float(config.get("residual_mult", 1.0)), tied_head=int(bool(config.get("tied_head", False))),
-      ff_unfiltered=int(bool(config.get("ff_unfiltered", False))))
+      ff_unfiltered=int(bool(config.get("ff_unfiltered", False))),
+      gated_residual=int(bool(config.get("gated_residual", False))),
+      bigram_buckets=int(bg["buckets"]) if bg else 0, bigram_mul_prev=int(bg["mul_prev"]) if bg else 0,
+      bigram_mul_cur=int(bg["mul_cur"]) if bg else 0, pos_rows=int(config.get("pos_rows", 0)))
     self.first_from_mlp = self.last_to_attn = False
     self.is_first = self.is_last = True
     self.desc, self._layers = d, lays

@@ -261,6 +261,67 @@ def random_pufivik_state(cfg: dict, seed: int = 0, dtype: torch.dtype = torch.bf
   return out
 
 
+def vusenex_param_shapes(cfg: dict) -> Dict[str, tuple]:
+  """name -> shape of every tensor of a Vusenex config.json (norms of the stream are single numbers)."""
+  D, V = cfg["width"], cfg["vocab"]
+  sh = {"embed": (V, D), "pos": (cfg["max_positions"], D), "final.norm": (), "head": (V, D)}
+  bg = (cfg.get("embedding") or {}).get("bigram")
+  if bg:
+    sh["bigram"] = (bg["buckets"] + 1, D)
+  for i, lc in enumerate(cfg["layers"]):
+    p, m = f"l{i}.", lc["mixer"]
+    sh.update({p + "norm1": (), p + "rg1": (D, D), p + "rg1.b": (D,)})
+    if lc["type"] == "attention":
+      H, G, dk = m["heads"], m["kv_heads"], m["dim"]
+      sh.update({p + "mix.q": (H * dk, D), p + "mix.q.b": (H * dk,), p + "mix.k": (G * dk, D), p + "mix.k.b": (G * dk,),
+                 p + "mix.q.norm": (H * dk,), p + "mix.k.norm": (G * dk,), p + "mix.r1": (H,), p + "mix.r2": (H,), p + "mix.o": (D, H * dk)})
+    else:
+      H, dk, dv, R = m["heads"], m["dim"], m["vdim"], m["kv_rank"]
+      sh.update({p + "mix.q": (H * dk, D), p + "mix.dkv": (R, D), p + "mix.dkv.norm": (R,), p + "mix.uk": (H * dk, R), p + "mix.uv": (H * dv, R),
+                 p + "mix.o": (D, H * dv)})
+    mlp = lc.get("mlp")
+    if mlp:
+      F, E = mlp["expert"]["ff"], mlp["router"]["experts"]
+      sh.update({p + "norm2": (), p + "rg2": (D, D), p + "rg2.b": (D,), p + "mlp.router": (E, D)})
+      for e in range(E):
+        sh.update({f"{p}mlp.e{e}.up": (F, D), f"{p}mlp.e{e}.down": (D, F)})
+      if mlp.get("shared"):
+        S = mlp["shared"]["ff"]
+        sh.update({p + "mlp.shared.up": (S, D), p + "mlp.shared.down": (D, S)})
+  return sh
+
+
+def random_vusenex_state(cfg: dict, seed: int = 0, dtype: torch.dtype = torch.bfloat16, gain: float = 1.0,
+                         device: str = "cpu") -> Dict[str, torch.Tensor]:
+  """Seeded random Vusenex weights: matrices N(0, gain^2 / in), the stream's norm numbers in (0.5, 1.5), q / k norm weights
+  1 + N(0, 0.1^2), biases N(0, 0.3^2), distance penalties r1 in (0.1, 0.9) and r2 in (0.05, 1), routers spread so that the
+  scores differ, table rows N(0, 1)."""
+  out = {}
+  for idx, (name, shape) in enumerate(sorted(vusenex_param_shapes(cfg).items())):
+    g = torch.Generator(device=device).manual_seed(seed * 1000003 + idx)
+    rn = lambda: torch.randn(shape, generator=g, device=device)  # noqa: E731
+    ru = lambda: torch.rand(shape, generator=g, device=device)  # noqa: E731
+    leaf = name.split(".")[-1]
+    if name in ("embed", "pos", "bigram"):
+      t = (0.6 if name == "embed" else 0.4) * rn()
+    elif leaf in ("norm1", "norm2") or name == "final.norm":
+      t = 0.5 + ru()
+    elif leaf == "norm":
+      t = 1.0 + 0.1 * rn()
+    elif leaf == "b":
+      t = 0.3 * rn()
+    elif leaf == "r1":
+      t = 0.1 + 0.8 * ru()
+    elif leaf == "r2":
+      t = 0.05 + 0.95 * ru()
+    elif leaf == "router":
+      t = 2.0 * gain * rn() / (shape[-1] ** 0.5)
+    else:
+      t = gain * rn() / (shape[-1] ** 0.5)
+    out[name] = t.to(dtype)
+  return out
+
+
 def write_random_checkpoint(path: Path, cfg: dict, seed: int = 0, std: float = 0.02,
                             norm_jitter: float = 0.0, shard_bytes: int = 4 << 30,
                             peaked_head: float = 0.0) -> Path:
@@ -275,6 +336,8 @@ def write_random_checkpoint(path: Path, cfg: dict, seed: int = 0, std: float = 0
     state = random_bibevik_state(cfg, seed=seed)
   elif cfg.get("architecture") == "Pufivik":
     state = random_pufivik_state(cfg, seed=seed)
+  elif cfg.get("architecture") == "Vusenex":
+    state = random_vusenex_state(cfg, seed=seed)
   else:
     state = random_hf_state(cfg, seed=seed, std=std, norm_jitter=norm_jitter, peaked_head=peaked_head)
   files, cur, cur_bytes = [], {}, 0

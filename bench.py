@@ -698,7 +698,7 @@ def run_family_compare(args):
   from xotorch_support_jetson_b200.pipeline import gpu_random_getter
   from xotorch_support_jetson_b200.shard import Shard
   from xotorch_support_jetson_b200.stage import StageRuntime
-  from xotorch_support_jetson_b200.synth import random_bibevik_state, random_pufivik_state, random_refatar_state
+  from xotorch_support_jetson_b200.synth import random_bibevik_state, random_pufivik_state, random_refatar_state, random_vusenex_state
   torch.cuda.set_device(0)
   dev = torch.device("cuda", 0)
   peaks = measured_peaks()
@@ -718,7 +718,7 @@ def run_family_compare(args):
     st = StageRuntime(Shard(mid, 0, nl - 1, nl), cfg, device=0, max_batch_tokens=cap, max_seqs=max_seqs,
                       max_tokens_per_seq=max(ctx + 2 * (K + W) + 64, cap), page_tokens=64)
     if mc.is_hybrid(cfg):
-      make = {"Bibevik": random_bibevik_state, "Pufivik": random_pufivik_state}.get(cfg["architecture"], random_refatar_state)
+      make = {"Bibevik": random_bibevik_state, "Pufivik": random_pufivik_state, "Vusenex": random_vusenex_state}.get(cfg["architecture"], random_refatar_state)
       st.load_state(make(raw, seed=0, device="cuda"))
     else:
       get, has = gpu_random_getter(raw, 0, 0.02, dev)

@@ -265,12 +265,12 @@ def bare(cfg, w):
   return w
 
 
-def planted(kind, width=32):
+def planted(kind, width=32, dim=12):
   """One attention layer in which the token with id 1 leaves a key that every later query scores far above all others and
   a large value: a query that misses it -- a page border, a border of the kernel's key passes, a lost cache row, the first
   position -- changes the logits by far more than rounding does."""
   if kind == "attention":
-    cfg = config([(kv_attn(heads=2, kv=1, dim=12, scale=1.0, coef=0.0), None)], width=width, vocab=50)
+    cfg = config([(kv_attn(heads=2, kv=1, dim=dim, scale=1.0, coef=0.0), None)], width=width, vocab=50)
   else:
     cfg = config([(latent(heads=2, dim=12, vdim=8, rank=16, scale=1.0), None)], width=width, vocab=50)
   w = bare(cfg, weights(cfg, seed=9))
@@ -280,7 +280,6 @@ def planted(kind, width=32):
   w["embed"][1, 0] = 6.0                       # the planted token: one large channel that no other token has
   w["embed"][1, 1] = 2.0
   if kind == "attention":
-    dim = 12
     w["l0.mix.q.norm"][:] = 1.0
     w["l0.mix.k.norm"][:] = 1.0
     w["l0.mix.q.b"][:] = 0.0
@@ -330,12 +329,13 @@ def test_far_key_at_page_and_pass_borders_and_first_positions(lib, kind):
   st.close()
 
 
-@pytest.mark.parametrize("kind,dtype", [("attention", "float32"), ("latent_attention", "float32"), ("attention", "bfloat16"), ("latent_attention", "bfloat16")])
-def test_far_key_among_hundreds(lib, kind, dtype):
+@pytest.mark.parametrize("kind,dtype,dim", [("attention", "float32", 12), ("latent_attention", "float32", 12), ("attention", "bfloat16", 12),
+                                            ("latent_attention", "bfloat16", 12), ("attention", "bfloat16", 64), ("attention", "bfloat16", 128)])
+def test_far_key_among_hundreds(lib, kind, dtype, dim):
   """The planted key lies 500 to 600 positions back, at the borders of the block's 512-key passes (and, in bf16 serving, of
-  the latent kernel's 64-key tiles and key shares)."""
-  cfg, w = planted(kind)
-  st = stage(cfg, w, dtype, page=8)
+  the 64-key tiles and key shares of the latent kernel and, with heads of 64 or 128, of the tensor-core attention kernels)."""
+  cfg, w = planted(kind, dim=dim)
+  st = stage(cfg, w, dtype, page=8 if dim == 12 else 64)
   for at in (3, 63, 64, 88, 89):
     ids = [(7 + 5 * i) % 48 + 2 for i in range(610)]
     ids[at] = 1
@@ -446,37 +446,43 @@ def test_router_groups_and_weights(lib):
 
 
 # ----------------------------------------------------------------------------- the serving engine and the command line
-def test_greedy_generation_through_the_serving_engine(lib, tmp_path, monkeypatch):
+def test_greedy_generation_through_the_serving_engine(lib, tmp_path):
+  """B200ShardInferenceEngine (infer_prompt / sample / infer_tensor, its request table and slot scheduler) on the registered
+  vusenex-tiny model, checkpoint written and loaded from disk, against greedy decoding of the oracle."""
+  from safetensors.torch import load_file
   from xotorch_support_jetson_b200.b200_engine import B200ShardInferenceEngine
-  from xotorch_support_jetson_b200.models import model_cards
-  from xotorch_support_jetson_b200.shard import Shard
-  from xotorch_support_jetson_b200.synth import SynthShardDownloader, random_vusenex_state
-  monkeypatch.setenv("XOT_HOME", str(tmp_path))
-  cfg = model_cards["vusenex-tiny"]["hf_config"]
-  nl = len(cfg["layers"])
-  shard = Shard("vusenex-tiny", 0, nl - 1, nl)
-  eng = B200ShardInferenceEngine(SynthShardDownloader(seed=4), dtype="float32")
-  prompt = np.array([toks(21, cfg["vocab"], seed=41)], dtype=np.int64)
+  from xotorch_support_jetson_b200.models import build_full_shard, model_cards
+  from xotorch_support_jetson_b200.synth import LocalShardDownloader
+  mid = "vusenex-tiny"
+  eng = B200ShardInferenceEngine(LocalShardDownloader(root=tmp_path, seed=2), device=0, max_seqs=4, max_tokens_per_seq=256,
+                                 max_batch_tokens=16, page_tokens=16, dtype="float32")
+  shard = build_full_shard(mid, "B200ShardInferenceEngine")
+  cfg = model_cards[mid]["hf_config"]
+  prompt = [3 + (11 * i) % 440 for i in range(37)]          # 37 tokens through 16-row native calls: chunked prefill
 
   async def go():
-    out, _ = await eng.infer_tensor("r1", shard, prompt)
-    ids = [int((await eng.sample(out, temp=0.0))[0])]
-    for _ in range(14):
-      out, _ = await eng.infer_tensor("r1", shard, np.array([[ids[-1]]], dtype=np.int64))
-      ids.append(int((await eng.sample(out, temp=0.0))[0]))
-    return ids
+    out, state = await eng.infer_prompt("g1", shard, "<ids:" + ",".join(map(str, prompt)) + ">")
+    ids, lg = [], [out]
+    for _ in range(12):
+      tok = await eng.sample(out, temp=0.0)
+      ids.append(int(tok.item()))
+      out, state = await eng.infer_tensor("g1", shard, tok.reshape(1, 1), state)
+      lg.append(out)
+    eng.end_request("g1")
+    return ids, lg
 
-  got = asyncio.run(go())
-  w = random_vusenex_state(cfg, seed=4)
-  seq = prompt[0].tolist()
-  want = []
-  for _ in range(15):
-    lg = O.forward(w, cfg, seq)[-1]
-    top2 = np.sort(lg)[-2:]
-    want.append((int(np.argmax(lg)), float(top2[1] - top2[0])))
-    seq.append(got[len(want) - 1])               # teacher-forced on the engine's choice: a near tie may differ once
-  for g, (t, margin) in zip(got, want):
-    assert g == t or margin < 1e-3
+  ids, lg = asyncio.run(go())
+  w = {}
+  for f in sorted((tmp_path / "synthetic--vusenex-tiny").glob("*.safetensors")):
+    w.update(load_file(str(f)))
+  seq = list(prompt)
+  for step, tok in enumerate(ids):
+    ref = logits(cfg, w, seq)[-1]
+    assert rel(torch.from_numpy(lg[step][0]).double(), ref) < TOL["float32"]
+    top2 = ref.topk(2).values
+    if float(top2[0] - top2[1]) > 1e-3:
+      assert tok == int(ref.argmax()), step
+    seq.append(tok)
 
 
 def test_trace_runner_on_a_model_folder(lib, tmp_path):

@@ -47,10 +47,13 @@ __device__ __forceinline__ uint32_t att_tile_off(int r, int c16) {
 //   sK, sV  : shared-memory byte addresses of the K / V tile
 //   krow0   : first key row (inside the tile) this warp handles; it handles NKB*16 rows
 //   key_abs0: absolute position of tile row 0;  lim0/lim1: last visible key of the thread's two rows
+//   dist    : nullptr, or {r1, r2} of row 0 then of row 1: r1 * ln(1 + r2 * (lim - key)) is taken off the scaled score
+//             (lim = the row's own position), in log2 units r1 * log2(1 + r2 * distance)
 template <int HD, int NKB>
 __device__ __forceinline__ void att_warp_block(const uint32_t (*qf)[4], uint32_t sK, uint32_t sV, int krow0, int key_abs0,
                                                int lim0, int lim1, float scale_log2, float (&mrow)[2],
-                                               float (&lrow)[2], float (*o)[4], float softcap = 0.f, bool p_split = false) {
+                                               float (&lrow)[2], float (*o)[4], float softcap = 0.f, bool p_split = false,
+                                               const float* dist = nullptr) {
   constexpr int KS = HD / 16;   // k-steps over the head dim
   constexpr int DT = HD / 8;    // output n-tiles over the head dim
   constexpr int NT = NKB * 2;   // score n-tiles (8 keys each)
@@ -84,6 +87,14 @@ __device__ __forceinline__ void att_warp_block(const uint32_t (*qf)[4], uint32_t
       for (int i = 0; i < 4; ++i) s[j][i] = cl * (1.0f - __fdividef(2.0f, 1.0f + exp2f(s[j][i] * ck)));
     } else {
       s[j][0] *= scale_log2; s[j][1] *= scale_log2; s[j][2] *= scale_log2; s[j][3] *= scale_log2;
+    }
+    if (dist != nullptr) {
+      const float d00 = (float)max(lim0 - k0, 0), d01 = (float)max(lim0 - k0 - 1, 0);
+      const float d10 = (float)max(lim1 - k0, 0), d11 = (float)max(lim1 - k0 - 1, 0);
+      s[j][0] = fmaf(-dist[0], __log2f(fmaf(dist[1], d00, 1.0f)), s[j][0]);
+      s[j][1] = fmaf(-dist[0], __log2f(fmaf(dist[1], d01, 1.0f)), s[j][1]);
+      s[j][2] = fmaf(-dist[2], __log2f(fmaf(dist[3], d10, 1.0f)), s[j][2]);
+      s[j][3] = fmaf(-dist[2], __log2f(fmaf(dist[3], d11, 1.0f)), s[j][3]);
     }
     if (k0 > lim0) s[j][0] = -INFINITY;
     if (k0 + 1 > lim0) s[j][1] = -INFINITY;
@@ -197,6 +208,8 @@ struct AttDecOpt {
   int v_wide;
   long long out_head_stride;
   int p_split;   // 1: the softmax weights enter the value product as hi + lo bf16 pairs (fp32-grade weights)
+  const float* r1;   // both or neither, one number per head: r1 * ln(1 + r2 * (position - key position)) is taken off the score
+  const float* r2;
 };
 struct QkvFin {
   const float* part;
@@ -330,6 +343,13 @@ __global__ void __launch_bounds__(160) xb_attn_decode_mma_kernel(
     float o[DT][4];
 #pragma unroll
     for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    float dist4[4] = {0.f, 0.f, 0.f, 0.f};   // the distance penalty of the thread's real row (the other is padding)
+    if (!FUSED && opt.r1 != nullptr) {   // (the fused form serves the Llama-shaped models, which have no such term)
+      const int hh = kvh * G + ((lane >> 2) < G ? (lane >> 2) : 0);
+      dist4[0] = opt.r1[hh];
+      dist4[1] = opt.r2[hh];
+    }
+    const float* distp = (!FUSED && opt.r1 != nullptr) ? dist4 : nullptr;
 
     int stage = 0;
     uint32_t phase = 0;
@@ -350,7 +370,7 @@ __global__ void __launch_bounds__(160) xb_attn_decode_mma_kernel(
       }
       if (key_abs0 + warp * 16 <= pos) {
         const uint32_t sK = smem_u32(stages + stage * Cfg::STAGE_BYTES);
-        att_warp_block<HD, 1>(qf, sK, sK + Cfg::TILE_BYTES, warp * 16, key_abs0, pos, pos, scale_log2, mrow, lrow, o, opt.softcap, opt.p_split != 0);
+        att_warp_block<HD, 1>(qf, sK, sK + Cfg::TILE_BYTES, warp * 16, key_abs0, pos, pos, scale_log2, mrow, lrow, o, opt.softcap, opt.p_split != 0, distp);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[stage]);
@@ -588,6 +608,8 @@ struct AttIo {
   int v_wide;
   long long out_head_stride;
   int p_split;   // 1: the softmax weights enter the value product as hi + lo bf16 pairs (fp32-grade weights): twice the PV MMAs
+  const float* r1;   // both or neither, one number per head: r1 * ln(1 + r2 * (query position - key position)) is taken off
+  const float* r2;   // the scaled (and capped) score
 };
 
 // EXT = false compiles the plain causal / windowed kernel (the AttIo options below sink are ignored).
@@ -804,7 +826,9 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
     }
     float m_used = -INFINITY;     // reference max (scaled, log2 units) that O and l are expressed against
     float l_sum = 0.f;
-    const float sl2 = (EXT && io.softcap > 0.f) ? 1.0f : scale_log2;                       // what turns a score in v[] into log2 units
+    const bool dist = EXT && io.r1 != nullptr;
+    const float dr1 = dist ? io.r1[kvh * G + gq] : 0.f, dr2 = dist ? io.r2[kvh * G + gq] : 0.f;
+    const float sl2 = (EXT && (io.softcap > 0.f || dist)) ? 1.0f : scale_log2;             // what turns a score in v[] into log2 units
     const float cl2 = io.softcap * 1.4426950408889634f;
     const float cap_k = io.softcap > 0.f ? 2.0f * scale_log2 / io.softcap : 0.f;  // raw product -> 2 s / cap in log2 units
     for (int kt = 0; kt < n_kt; ++kt) {
@@ -826,6 +850,17 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
           asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(__uint_as_float(v[j]) * cap_k));
           asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(1.0f + ex));
           v[j] = __float_as_uint(fmaf(-2.0f * cl2, rc, cl2));
+        }
+      }
+      if (dist) {
+        // distance penalty in log2 units, r1 * log2(1 + r2 * (row position - key position)), off the scaled score: the
+        // softmax below takes v[] as it is (sl2 = 1).  Keys behind the row's position are masked further down.
+        const float in2 = io.softcap > 0.f ? 1.0f : scale_log2;
+#pragma unroll
+        for (int j = 0; j < XB_ATT_TILE; ++j) {
+          float lg;
+          asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(fmaf(dr2, (float)max(lim - (key0 + j), 0), 1.0f)));
+          v[j] = __float_as_uint(fmaf(-dr1, lg, __uint_as_float(v[j]) * in2));
         }
       }
       // only tiles that reach past the first row's position, or (with a window) back beyond the last row's window,

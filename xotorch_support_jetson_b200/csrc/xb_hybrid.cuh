@@ -339,8 +339,7 @@ static int hy_create_softmax(xb_engine* e, int i, bool own, uint64_t& wbytes, ui
   if (c.s_vmix && (size_t)(G * dv) > hy->maxGV) hy->maxGV = (size_t)(G * dv);
   // bf16 serving, key and value heads of one size (64 or 128), at most 8 query heads per key head: prompts run through the
   // engine's tcgen05 attention (sink, score cap and the wide value rows of mixed heads as its options)
-  // (the tensor-core kernels know no distance penalty: such layers run the per-(token, head) kernel)
-  l.tc_attn = !d.compute_fp32 && dk == dv && (dk == 64 || dk == 128) && H / G <= 8 && !c.s_dist_bias;
+  l.tc_attn = !d.compute_fp32 && dk == dv && (dk == 64 || dk == 128) && H / G <= 8;
   if (l.tc_attn && qa > hy->maxQG) hy->maxQG = qa;
   wbytes += ((size_t)l.n_in * D + D * l.n_o) * 2;
   kvpos += (uint64_t)G * (dk + dv) * (d.compute_fp32 ? 4 : 2);
@@ -1417,7 +1416,7 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, i
     // mixed heads multiply the blocks by the key heads: fewer splits keep the grid near one wave
     int ns = l.v_all ? hy->dec_splits / G : hy->dec_splits;
     ns = ns < 1 ? 1 : ns;
-    const AttDecOpt dopt{c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : 0, (long long)dvo, hy->p_split};
+    const AttDecOpt dopt{c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : 0, (long long)dvo, hy->p_split, opt.r1, opt.r2};
     bf16* dst = post ? reinterpret_cast<bf16*>(hy->o) : reinterpret_cast<bf16*>(hy->a1);
     if (dk == 128) XB_TRY(hy_attn_dec<128>(e, l, m, T, hy->qg, dst, H, G, c.s_scale, ns, dopt, st));
     else XB_TRY(hy_attn_dec<64>(e, l, m, T, hy->qg, dst, H, G, c.s_scale, ns, dopt, st));
@@ -1427,7 +1426,7 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, i
   if (tc) {
     HyAttnIn in;
     in.tile_start = m.tile_start; in.tile_len = m.tile_len; in.n_tiles = n_tiles; in.q = hy->qg;
-    in.io = AttIo{(long long)H * dk, nullptr, nullptr, 0, c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : 0, (long long)dvo, hy->p_split};
+    in.io = AttIo{(long long)H * dk, nullptr, nullptr, 0, c.s_sink ? l.sink : nullptr, c.s_softcap, l.v_all ? 1 : 0, (long long)dvo, hy->p_split, opt.r1, opt.r2};
     bf16* dst = post ? reinterpret_cast<bf16*>(hy->o) : reinterpret_cast<bf16*>(hy->a1);
     if (dk == 128) XB_TRY(hy_attn_tc_any<128>(e, l, m, in, dst, H, G, c.s_scale, l.v_all ? G : 1, st));
     else XB_TRY(hy_attn_tc_any<64>(e, l, m, in, dst, H, G, c.s_scale, l.v_all ? G : 1, st));
@@ -1485,6 +1484,10 @@ static int hy_run_branchnorm_t(xb_engine* e, int T, int n_seqs, int n_tiles, voi
     a.x = hy->x; a.m1 = y; a.m2 = hy_none(); a.m3 = hy_none(); a.s1 = 1.f; a.s2 = 0.f; a.bw = bw; a.bw_one = 0.f; a.nw = nw; a.hn = hy->hn;
     a.xa = a1; a.ha = nullptr; a.eps = d.norm_eps; a.D = D; a.plain_add = 0; a.nw_mode = d.norm_scalar ? 2 : 1; a.groups = 1; a.res_mult = 1.f; a.ext = 0;
     a.gate = off_gate >= 0 ? P : hy_none(); a.gate_off = off_gate >= 0 ? off_gate : 0; a.bw_mode = d.norm_scalar ? 2 : 1;
+    // prompts whose branch and gate came back as bf16 matrices: eight channels per thread
+    const bool gate_ok = off_gate < 0 || (P.h != nullptr && P.ld % 8 == 0 && off_gate % 8 == 0);
+    if (!few && y.h != nullptr && y.bias == nullptr && y.ld % 8 == 0 && gate_ok && D % 8 == 0)
+      return hy_launch(e, hy_row_op_gated_vec_kernel<AT>, dim3(T), dim3(256), (size_t)D * sizeof(float), st, a);
     if (few) return hy_launch(e, hy_row_op_gated_kernel<AT, 1024>, dim3(T), dim3(1024), (size_t)D * sizeof(float), st, a);
     return hy_launch(e, hy_row_op_gated_kernel<AT, 256>, dim3(T), dim3(256), (size_t)D * sizeof(float), st, a);
   };

@@ -374,6 +374,63 @@ template <> __device__ __forceinline__ void hy_st8a<float>(float* p, const float
 template <> __device__ __forceinline__ void hy_st8a<bf16>(bf16* p, const float* v) {
   *reinterpret_cast<uint4*>(p) = make_uint4(f2_to_bf2(v[0], v[1]), f2_to_bf2(v[2], v[3]), f2_to_bf2(v[4], v[5]), f2_to_bf2(v[6], v[7]));
 }
+// hy_row_op_gated_kernel for prompts whose branch and gate are bf16 matrices out of the tensor-core Linear: eight channels
+// per thread, 16-byte loads, the new row written as the stream and as the next Linear input in one pass.  D, the pitches and
+// gate_off are multiples of 8; the branch carries no bias, the gate's (fp32) is added on read.
+template <typename AT>
+__global__ void __launch_bounds__(256) hy_row_op_gated_vec_kernel(RowOpArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int NT = 256;
+  extern __shared__ __align__(16) float row[];
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  const int D = a.D;
+  float* x = a.x + t * D;
+  const bf16* br = a.m1.h + t * a.m1.ld;
+  const bool gated = a.gate.h != nullptr;
+  const bf16* gr = gated ? a.gate.h + t * a.gate.ld + a.gate_off : nullptr;
+  const float* gb = (gated && a.gate.bias != nullptr) ? a.gate.bias + a.gate_off : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < D; i += NT * 8) {
+    float v[8];
+    hy_load8(br + i, nullptr, v);
+    if (gated) {
+      float g[8];
+      hy_load8(gr + i, gb != nullptr ? gb + i : nullptr, g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] *= hy_sigmoid(g[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
+    hy_st8f(row + i, v);
+  }
+  const float inv = 1.0f / sqrtf(block_sum<NT>(ss, red) / (float)D + a.eps);
+  ss = 0.f;
+  for (int i = threadIdx.x * 8; i < D; i += NT * 8) {   // a thread revisits the channels it wrote itself
+    float v[8], xv[8];
+    hy_ld8f(row + i, v);
+    hy_ld8f(x + i, xv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      xv[j] = xv[j] + v[j] * inv * (a.bw_mode == 2 ? a.bw[0] : a.bw[i + j]);
+      ss = fmaf(xv[j], xv[j], ss);
+    }
+    hy_st8f(x + i, xv);
+    if (a.xa != nullptr) hy_st8a<AT>(reinterpret_cast<AT*>(a.xa) + t * D + i, xv);
+    if (a.nw != nullptr) hy_st8f(row + i, xv);
+  }
+  if (a.nw == nullptr) return;
+  const float inv2 = 1.0f / sqrtf(block_sum<NT>(ss, red) / (float)D + a.eps);
+  for (int i = threadIdx.x * 8; i < D; i += NT * 8) {
+    float v[8];
+    hy_ld8f(row + i, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = v[j] * inv2 * hy_norm_weight(a.nw, a.nw_mode, i + j);
+    hy_st8f(a.hn + t * D + i, v);
+  }
+}
+
 template <typename AT>
 __global__ void __launch_bounds__(256) hy_row_op_vec_kernel(RowOpArgs a) {
   pdl_launch_dependents();

@@ -87,6 +87,7 @@ struct HyModel {
   float* vfirst = nullptr;              // values of the first blending layer for the tokens of this step [T, G * dv]
   size_t maxGV = 0;
   int use_gather = 1;                   // XB_HY_GATHER=0: experts always as one wide Linear pair (A/B)
+  int fuse_router = 1;                  // XB_HY_FUSE_ROUTER=0: steps of few rows form the router's logits and route in two kernels (A/B)
   int p_split = 1;                      // XB_HY_P_SPLIT=0: rotary-position attention rounds its softmax weights to bf16 (A/B)
   int dec_splits = 1;                   // key splits of this step's single-token attention (hy_kv_splits)
   bool pdl_now = false;
@@ -655,6 +656,8 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
     if (ta != nullptr && ta[0] == '0') hy->use_tc_attn = 0;
     const char* ga = getenv("XB_HY_GATHER");
     if (ga != nullptr && ga[0] == '0') hy->use_gather = 0;
+    const char* fr = getenv("XB_HY_FUSE_ROUTER");
+    if (fr != nullptr && fr[0] == '0') hy->fuse_router = 0;
     const char* ps = getenv("XB_HY_P_SPLIT");
     if (ps != nullptr && ps[0] == '0') hy->p_split = 0;
     const char* lp = getenv("XB_HY_LPC");
@@ -1224,7 +1227,7 @@ static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, const void* xin
     XB_TRY(hy_launch(e, hy_router_logits_kernel<AT, 1>, dim3((unsigned)(((long long)T * c.n_experts + 7) / 8)), dim3(256), 0, st,
                      reinterpret_cast<const AT*>(xin), (long long)D, (const bf16*)l.w_router, hy->m2, T, c.n_experts, D));
     const size_t rs = (size_t)4 * (2 * c.n_experts + (c.groups > 0 ? c.groups : 1)) * sizeof(float);
-    XB_TRY(hy_launch(e, hy_route_kernel, dim3((T + 3) / 4), dim3(128), rs, st, hy_plain(hy->m2, c.n_experts), c.n_experts, c.top, c.groups,
+    XB_TRY(hy_launch(e, hy_route_kernel, dim3((T + 3) / 4), dim3(128), rs, st, (const float*)hy->m2, c.n_experts, c.top, c.groups,
                      c.keep_groups, c.route_scale, hy->gw, T, c.route_score, c.group_score, c.route_norm));
     const long long nu = (long long)T * c.top * c.ff, nd = (long long)T * D;
     XB_TRY(hy_launch(e, hy_moe_gather_up_kernel<AT>, dim3((unsigned)((nu + 7) / 8)), dim3(256), 0, st, reinterpret_cast<const AT*>(xin), (long long)D,
@@ -1248,18 +1251,23 @@ static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, const void* xin
       XB_TRY(hy_launch(e, hy_glu_clamp_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, U, c.ff, c.ff_limit, a2, (long long)l.n_dn, T));
   } else {
     // router in fp32 whatever the serving type: fp32 accumulation of the products, fp32 logits
-    if (T <= 64) {   // few rows: a warp per (token, expert)
-      XB_TRY(hy_launch(e, hy_router_logits_kernel<AT, 1>, dim3((unsigned)(((long long)T * c.n_experts + 7) / 8)), dim3(256), 0, st,
-                       reinterpret_cast<const AT*>(xin), (long long)D, (const bf16*)l.w_router, hy->m2, T, c.n_experts, D));
+    if (T <= 64 && hy->fuse_router) {   // few rows: logits and routing of a token in one block
+      const size_t rs1 = (size_t)(3 * c.n_experts + (c.groups > 0 ? c.groups : 1)) * sizeof(float);
+      XB_TRY(hy_launch(e, hy_router_route_kernel<AT>, dim3(T), dim3(256), rs1, st, reinterpret_cast<const AT*>(xin), (long long)D, (const bf16*)l.w_router, D,
+                       c.n_experts, c.top, c.groups, c.keep_groups, c.route_scale, hy->gw, c.route_score, c.group_score, c.route_norm));
     } else {
-      const int chunks = (c.n_experts + 7) / 8;
-      XB_TRY(hy_launch(e, hy_router_logits_kernel<AT, 8>, dim3((unsigned)(((long long)T * chunks + 7) / 8)), dim3(256), 0, st,
-                       reinterpret_cast<const AT*>(xin), (long long)D, (const bf16*)l.w_router, hy->m2, T, c.n_experts, D));
+      if (T <= 64) {   // few rows: a warp per (token, expert)
+        XB_TRY(hy_launch(e, hy_router_logits_kernel<AT, 1>, dim3((unsigned)(((long long)T * c.n_experts + 7) / 8)), dim3(256), 0, st,
+                         reinterpret_cast<const AT*>(xin), (long long)D, (const bf16*)l.w_router, hy->m2, T, c.n_experts, D));
+      } else {
+        const int chunks = (c.n_experts + 7) / 8;
+        XB_TRY(hy_launch(e, hy_router_logits_kernel<AT, 8>, dim3((unsigned)(((long long)T * chunks + 7) / 8)), dim3(256), 0, st,
+                         reinterpret_cast<const AT*>(xin), (long long)D, (const bf16*)l.w_router, hy->m2, T, c.n_experts, D));
+      }
+      const size_t rs = (size_t)4 * (2 * c.n_experts + (c.groups > 0 ? c.groups : 1)) * sizeof(float);
+      XB_TRY(hy_launch(e, hy_route_kernel, dim3((T + 3) / 4), dim3(128), rs, st, (const float*)hy->m2, c.n_experts, c.top, c.groups, c.keep_groups,
+                       c.route_scale, hy->gw, T, c.route_score, c.group_score, c.route_norm));
     }
-    const LinOut z = hy_plain(hy->m2, c.n_experts);
-    const size_t rs = (size_t)4 * (2 * c.n_experts + (c.groups > 0 ? c.groups : 1)) * sizeof(float);
-    XB_TRY(hy_launch(e, hy_route_kernel, dim3((T + 3) / 4), dim3(128), rs, st, z, c.n_experts, c.top, c.groups, c.keep_groups, c.route_scale,
-                     hy->gw, T, c.route_score, c.group_score, c.route_norm));
     const long long n = (long long)T * l.n_dn;
     const int sf = c.shared_ff > 0 ? c.shared_ff : 0;
     if (c.ff_act == XB_ACT_GELU) {   // experts without a gate projection
@@ -1397,10 +1405,19 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, i
   const int rope_by = T >= 512 ? 1 : (units + 255) / 256;
   const bool rope_vec = tc && P.h != nullptr && P.bias == nullptr && P.ld % 8 == 0 && dk % 8 == 0 && dv % 8 == 0 &&
                         c.s_rot_dims % (r.half ? 16 : 8) == 0 && (G * dv) % 8 == 0;
-  if (c.s_qk_norm != 0 || c.s_v_is_k != 0 || c.s_qtemp_every > 0)   // no rotation: whole-projection norms, temperature, append
-    XB_TRY(hy_launch(e, hy_qk_prep_kernel<KT>, dim3(T), dim3(256), (size_t)(H + G) * dk * sizeof(float), st, P, l.off_q, l.off_k, l.off_v, H, G, dk, dv,
-                     c.s_qk_norm ? (const float*)l.qn : (const float*)nullptr, c.s_qk_norm ? (const float*)l.kn : (const float*)nullptr, hy->d.norm_eps,
-                     c.s_qtemp_coef, c.s_qtemp_every, hy->qa, (tc || dec) ? hy->qg : (bf16*)nullptr, (KT*)l.k_pool, (KT*)l.v_pool, m));
+  if (c.s_qk_norm != 0 || c.s_v_is_k != 0 || c.s_qtemp_every > 0) {   // no rotation: whole-projection norms, temperature, append
+    const float* qn = c.s_qk_norm ? (const float*)l.qn : (const float*)nullptr;
+    const float* kn = c.s_qk_norm ? (const float*)l.kn : (const float*)nullptr;
+    float* qa = (tc || dec) ? (float*)nullptr : hy->qa;          // fp32 queries for the per-(token, head) kernel only
+    bf16* qg = (tc || dec) ? hy->qg : (bf16*)nullptr;
+    const size_t sm = (size_t)(H + G) * dk * sizeof(float);
+    if (T <= 64)
+      XB_TRY(hy_launch(e, hy_qk_prep_kernel<KT, 1024>, dim3(T), dim3(1024), sm, st, P, l.off_q, l.off_k, l.off_v, H, G, dk, dv, qn, kn, hy->d.norm_eps,
+                       c.s_qtemp_coef, c.s_qtemp_every, qa, qg, (KT*)l.k_pool, (KT*)l.v_pool, m));
+    else
+      XB_TRY(hy_launch(e, hy_qk_prep_kernel<KT, 256>, dim3(T), dim3(256), sm, st, P, l.off_q, l.off_k, l.off_v, H, G, dk, dv, qn, kn, hy->d.norm_eps,
+                       c.s_qtemp_coef, c.s_qtemp_every, qa, qg, (KT*)l.k_pool, (KT*)l.v_pool, m));
+  }
   else if (rope_vec)   // a prompt whose projection came back as a bf16 matrix: 16 bytes per thread
     XB_TRY(hy_launch(e, hy_rope_append_vec_kernel, dim3(T), dim3(256), 0, st, P.h, P.ld, l.off_q, l.off_k, l.off_v, H, G, dk, dv, r, hy->qg,
                      (bf16*)l.k_pool, (bf16*)l.v_pool, l.v_all ? 1 : 0, (const float*)l.vmix, hy->vfirst, l.vmode, m));

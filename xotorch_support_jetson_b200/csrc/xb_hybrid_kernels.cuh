@@ -1314,9 +1314,10 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
 //   k_pool [page][G][token][dk]    = the finished keys
 //   v_pool [page][G][token][dv]    = P[t, off_v ...]: the value projection, or with off_v = off_k (dv = dk) the keys as they were
 //                                    projected, before the norm
-// Everything after the projection is fp32.
-template <typename KT>
-__global__ void __launch_bounds__(256) hy_qk_prep_kernel(LinOut P, int off_q, int off_k, int off_v, int H, int G, int dk, int dv,
+// Everything after the projection is fp32.  qa may be nullptr (a tensor-core kernel reads qg instead).  NT threads: 256 for
+// prompts, 1024 in steps of few rows, where the reads of the projection's split-K planes are what takes the time.
+template <typename KT, int NT>
+__global__ void __launch_bounds__(NT) hy_qk_prep_kernel(LinOut P, int off_q, int off_k, int off_v, int H, int G, int dk, int dv,
                                                          const float* __restrict__ qn, const float* __restrict__ kn, float eps,
                                                          float temp_coef, int temp_every, float* __restrict__ qa, bf16* __restrict__ qg,
                                                          KT* __restrict__ k_pool, KT* __restrict__ v_pool, BatchMeta m) {
@@ -1328,26 +1329,26 @@ __global__ void __launch_bounds__(256) hy_qk_prep_kernel(LinOut P, int off_q, in
   const int nq = H * dk, nk = G * dk, nv = G * dv;
   const int s = m.tok_seq[row], pos = m.tok_pos[row];
   float sq = 0.f, sk = 0.f;
-  for (int i = threadIdx.x; i < nq; i += 256) { const float v = lin_at(P, row, off_q + i); qk[i] = v; sq = fmaf(v, v, sq); }
-  for (int i = threadIdx.x; i < nk; i += 256) { const float v = lin_at(P, row, off_k + i); qk[nq + i] = v; sk = fmaf(v, v, sk); }
+  for (int i = threadIdx.x; i < nq; i += NT) { const float v = lin_at(P, row, off_q + i); qk[i] = v; sq = fmaf(v, v, sq); }
+  for (int i = threadIdx.x; i < nk; i += NT) { const float v = lin_at(P, row, off_k + i); qk[nq + i] = v; sk = fmaf(v, v, sk); }
   float qs = 1.f, ks = 1.f;
-  if (qn != nullptr) qs = 1.0f / sqrtf(block_sum<256>(sq, red) / (float)nq + eps);
-  if (kn != nullptr) ks = 1.0f / sqrtf(block_sum<256>(sk, red) / (float)nk + eps);
+  if (qn != nullptr) qs = 1.0f / sqrtf(block_sum<NT>(sq, red) / (float)nq + eps);
+  if (kn != nullptr) ks = 1.0f / sqrtf(block_sum<NT>(sk, red) / (float)nk + eps);
   __syncthreads();
   const float temp = temp_every > 0 ? 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f) : 1.0f;
-  for (int i = threadIdx.x; i < nq; i += 256) {
+  for (int i = threadIdx.x; i < nq; i += NT) {
     const float v = qn != nullptr ? qk[i] * qs * qn[i] * temp : qk[i] * temp;
-    qa[(long long)row * nq + i] = v;
+    if (qa != nullptr) qa[(long long)row * nq + i] = v;
     if (qg != nullptr) qg[(long long)row * nq + i] = f2bf(v);
   }
   const long long pg = m.page_table[(long long)m.seq_slot[s] * m.max_pages + pos / m.page_tokens];
   const int ip = pos % m.page_tokens;
-  for (int i = threadIdx.x; i < nk; i += 256) {
+  for (int i = threadIdx.x; i < nk; i += NT) {
     const int g = i / dk, c = i - g * dk;
     const float v = kn != nullptr ? qk[nq + i] * ks * kn[i] : qk[nq + i];
     act_store<KT>(k_pool + ((pg * G + g) * m.page_tokens + ip) * dk + c, v);
   }
-  for (int i = threadIdx.x; i < nv; i += 256) {
+  for (int i = threadIdx.x; i < nv; i += NT) {
     const int g = i / dv, c = i - g * dv;
     const float v = off_v == off_k ? qk[nq + i] : lin_at(P, row, off_v + i);
     act_store<KT>(v_pool + ((pg * G + g) * m.page_tokens + ip) * dv + c, v);
@@ -2051,20 +2052,12 @@ __global__ void __launch_bounds__(256) hy_router_logits_kernel(const AT* __restr
 // score_mode: XB_ROUTE_SIGMOID, or XB_ROUTE_SOFTMAX = softmax of the logits over all experts.  group_mode: XB_GROUP_TOP2 as above,
 // or XB_GROUP_MAX = a group is worth its best score.  renorm: the chosen experts' scores are divided by their sum (+ 1e-20)
 // before the scale.
-__global__ void __launch_bounds__(128) hy_route_kernel(LinOut z, int E, int top, int groups, int keep, float scale, float* __restrict__ gw, int T,
-                                                       int score_mode, int group_mode, int renorm) {
-  pdl_launch_dependents();
-  pdl_wait();
-  extern __shared__ float rsm[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long t = (long long)blockIdx.x * 4 + warp;
-  if (t >= T) return;
-  float* sc = rsm + (size_t)warp * (2 * E + (groups > 0 ? groups : 1));
-  float* el = sc + E;      // eligible score, or -1 once taken / not eligible
-  float* gs = el + E;
+__device__ __forceinline__ void hy_route_token(const float* __restrict__ zrow, float* sc, float* el, float* gs, int E, int top, int groups, int keep,
+                                               float scale, float* __restrict__ gwrow, int score_mode, int group_mode, int renorm) {
+  const int lane = threadIdx.x & 31;
   if (score_mode == XB_ROUTE_SOFTMAX) {
     float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) { const float v = lin_at(z, t, e); sc[e] = v; mx = fmaxf(mx, v); }
+    for (int e = lane; e < E; e += 32) { const float v = zrow[e]; sc[e] = v; mx = fmaxf(mx, v); }
     mx = warp_max(mx);
     float sum = 0.f;
     for (int e = lane; e < E; e += 32) { const float v = expf(sc[e] - mx); sc[e] = v; sum += v; }
@@ -2072,7 +2065,7 @@ __global__ void __launch_bounds__(128) hy_route_kernel(LinOut z, int E, int top,
     for (int e = lane; e < E; e += 32) { const float v = sc[e] / sum; sc[e] = v; el[e] = v; }
   } else {
     for (int e = lane; e < E; e += 32) {
-      const float v = hy_sigmoid(lin_at(z, t, e));
+      const float v = hy_sigmoid(zrow[e]);
       sc[e] = v;
       el[e] = v;
     }
@@ -2098,7 +2091,7 @@ __global__ void __launch_bounds__(128) hy_route_kernel(LinOut z, int E, int top,
     }
     __syncwarp();
   }
-  for (int e = lane; e < E; e += 32) gw[t * E + e] = 0.f;
+  for (int e = lane; e < E; e += 32) gwrow[e] = 0.f;
   float tot = 0.f;   // sum of the chosen scores (every lane follows the same picks)
   for (int r = 0; r < top; ++r) {
     float bv = -1.f;
@@ -2113,14 +2106,58 @@ __global__ void __launch_bounds__(128) hy_route_kernel(LinOut z, int E, int top,
     }
     if (bi >= E || bv < 0.f) break;
     tot += bv;
-    if (lane == 0) { gw[t * E + bi] = sc[bi] * scale; el[bi] = -1.f; }
+    if (lane == 0) { gwrow[bi] = sc[bi] * scale; el[bi] = -1.f; }
     __syncwarp();
   }
   if (renorm) {
     const float inv = 1.0f / (tot + 1e-20f);
     __syncwarp();
-    for (int e = lane; e < E; e += 32) gw[t * E + e] *= inv;   // the entries of experts that were not chosen are zero
+    for (int e = lane; e < E; e += 32) gwrow[e] *= inv;   // the entries of experts that were not chosen are zero
   }
+}
+__global__ void __launch_bounds__(128) hy_route_kernel(const float* __restrict__ z, int E, int top, int groups, int keep, float scale,
+                                                       float* __restrict__ gw, int T, int score_mode, int group_mode, int renorm) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float rsm[];
+  const int warp = threadIdx.x >> 5;
+  const long long t = (long long)blockIdx.x * 4 + warp;
+  if (t >= T) return;
+  float* sc = rsm + (size_t)warp * (2 * E + (groups > 0 ? groups : 1));
+  hy_route_token(z + t * E, sc, sc + E, sc + 2 * E, E, top, groups, keep, scale, gw + t * E, score_mode, group_mode, renorm);
+}
+// Steps of few rows: logits and routing of a token in ONE block of eight warps.  Warp w forms the fp32 logits of experts
+// w, w + 8, ... (16-byte weight loads, fp32 sums, the order of hy_router_logits_kernel<AT, 1>), then the first warp routes.
+// Shared memory: 3 * E + groups floats.  grid (T), 256 threads.
+template <typename AT>
+__global__ void __launch_bounds__(256) hy_router_route_kernel(const AT* __restrict__ x, long long ldx, const bf16* __restrict__ w, int K, int E, int top,
+                                                              int groups, int keep, float scale, float* __restrict__ gw, int score_mode, int group_mode,
+                                                              int renorm) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float rsm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long t = blockIdx.x;
+  const AT* xr = x + t * ldx;
+  const bool vec = (K & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+  for (int e = warp; e < E; e += 8) {
+    const bf16* wr = w + (long long)e * K;
+    float acc = 0.f;
+    if (vec) {
+      for (int k = lane * 8; k < K; k += 256) {
+        float wv[8];
+        hy_load8(wr + k, nullptr, wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = fmaf(act_load<AT>(xr + k + i), wv[i], acc);
+      }
+    } else {
+      for (int k = lane; k < K; k += 32) acc = fmaf(act_load<AT>(xr + k), bf2f(wr[k]), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) rsm[e] = acc;
+  }
+  __syncthreads();
+  if (warp == 0) hy_route_token(rsm, rsm + E, rsm + 2 * E, rsm + 3 * E, E, top, groups, keep, scale, gw + t * E, score_mode, group_mode, renorm);
 }
 
 // U carries, expert after expert, [gate_e (f) | up_e (f)], then the shared expert's [gate (sf) | up (sf)].

@@ -193,8 +193,8 @@ _VUSENEX_TINY = _vusenex(160, 448, [
 # layers of 16 heads over a latent of 256, 16 experts of 512 of which a token uses four (the width of four of them plus the
 # shared expert = half of Llama's feed-forward)
 _VUSENEX_1B = _vusenex(2048, 128256, [
-  (("attention", _kv_attn(32, 8, 64, coef=0.3, every=128), _gelu_experts(16, 4, 512, 4, 3, 2048)) if i % 4 in (0, 3) else
-   ("latent_attention", _plain_latent(16, 64, 128, 256), _gelu_experts(16, 4, 512, 4, 3, 2048))) for i in range(16)], max_pos=8192, buckets=65521)
+  (("attention", _kv_attn(32, 8, 64, coef=0.25, every=96), _gelu_experts(16, 4, 512, 4, 2, 2048)) if i % 4 in (0, 3) else
+   ("latent_attention", _plain_latent(16, 64, 128, 256), _gelu_experts(16, 4, 512, 4, 2, 2048))) for i in range(16)], max_pos=8192, buckets=65521)
 
 # model id -> {layers, repo:{EngineClassName: hf repo}, hf_config}
 model_cards = {

@@ -1411,7 +1411,15 @@ static int hy_softmax_mixer(xb_engine* e, const HyLayer& l, int T, int n_seqs, i
     float* qa = (tc || dec) ? (float*)nullptr : hy->qa;          // fp32 queries for the per-(token, head) kernel only
     bf16* qg = (tc || dec) ? hy->qg : (bf16*)nullptr;
     const size_t sm = (size_t)(H + G) * dk * sizeof(float);
-    if (T <= 64)
+    bool vec8 = false;   // a prompt whose projection came back as a bf16 matrix, bf16 pools: 16 bytes per thread
+    if constexpr (std::is_same<KT, bf16>::value)
+      vec8 = T > 64 && qg != nullptr && qa == nullptr && P.h != nullptr && P.ld % 8 == 0 && dk % 8 == 0 && dv % 8 == 0 && l.off_q % 8 == 0 &&
+             l.off_k % 8 == 0 && l.off_v % 8 == 0;
+    if (vec8) {
+      if constexpr (std::is_same<KT, bf16>::value)
+        XB_TRY(hy_launch(e, hy_qk_prep_vec_kernel, dim3(T), dim3(256), sm, st, P.h, P.ld, P.bias, l.off_q, l.off_k, l.off_v, H, G, dk, dv, qn, kn,
+                         hy->d.norm_eps, c.s_qtemp_coef, c.s_qtemp_every, qg, (bf16*)l.k_pool, (bf16*)l.v_pool, m));
+    } else if (T <= 64)
       XB_TRY(hy_launch(e, hy_qk_prep_kernel<KT, 1024>, dim3(T), dim3(1024), sm, st, P, l.off_q, l.off_k, l.off_v, H, G, dk, dv, qn, kn, hy->d.norm_eps,
                        c.s_qtemp_coef, c.s_qtemp_every, qa, qg, (KT*)l.k_pool, (KT*)l.v_pool, m));
     else

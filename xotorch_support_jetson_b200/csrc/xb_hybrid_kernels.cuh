@@ -1355,6 +1355,74 @@ __global__ void __launch_bounds__(NT) hy_qk_prep_kernel(LinOut P, int off_q, int
   }
 }
 
+// The same arithmetic on 16-byte accesses, for prompts whose projection came back as ONE bf16 matrix and whose pools are bf16:
+// eight neighbouring channels per thread.  off_q, off_k, off_v, dk, dv and the projection's row pitch are multiples of 8;
+// the finished queries leave as bf16 rows (qg).  One block of 256 threads per token.
+__device__ __forceinline__ uint4 hy_pack8(const float* y);   // eight floats as bf16 neighbours (below)
+__global__ void __launch_bounds__(256) hy_qk_prep_vec_kernel(const bf16* __restrict__ P, long long ldp, const float* __restrict__ bias, int off_q, int off_k,
+                                                             int off_v, int H, int G, int dk, int dv, const float* __restrict__ qn,
+                                                             const float* __restrict__ kn, float eps, float temp_coef, int temp_every,
+                                                             bf16* __restrict__ qg, bf16* __restrict__ k_pool, bf16* __restrict__ v_pool, BatchMeta m) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float qk[];
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int nq = H * dk, nk = G * dk, nv = G * dv;
+  const int s = m.tok_seq[row], pos = m.tok_pos[row];
+  const bf16* prow = P + (long long)row * ldp;
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x * 8; i < nq + nk; i += 256 * 8) {
+    const int col = i < nq ? off_q + i : off_k + (i - nq);
+    float v[8];
+    hy_load8(prow + col, bias != nullptr ? bias + col : nullptr, v);
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
+    if (i < nq) sq += ss; else sk += ss;
+    hy_st8f(qk + i, v);
+  }
+  float qs = 1.f, ks = 1.f;
+  if (qn != nullptr) qs = 1.0f / sqrtf(block_sum<256>(sq, red) / (float)nq + eps);
+  if (kn != nullptr) ks = 1.0f / sqrtf(block_sum<256>(sk, red) / (float)nk + eps);
+  __syncthreads();
+  const float temp = temp_every > 0 ? 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f) : 1.0f;
+  const long long pg = m.page_table[(long long)m.seq_slot[s] * m.max_pages + pos / m.page_tokens];
+  const int ip = pos % m.page_tokens;
+  for (int i = threadIdx.x * 8; i < nq + nk; i += 256 * 8) {   // a thread revisits the channels it wrote itself
+    float v[8], w[8];
+    hy_ld8f(qk + i, v);
+    if (i < nq) {
+      if (qn != nullptr) {
+        hy_ld8f(qn + i, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = v[j] * qs * w[j] * temp;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] *= temp;
+      }
+      *reinterpret_cast<uint4*>(qg + (long long)row * nq + i) = hy_pack8(v);
+    } else {
+      const int ik = i - nq, g = ik / dk, c = ik - g * dk;
+      if (off_v == off_k)   // the values are the keys as projected
+        *reinterpret_cast<uint4*>(v_pool + ((pg * G + g) * m.page_tokens + ip) * dv + c) = hy_pack8(v);
+      if (kn != nullptr) {
+        hy_ld8f(kn + ik, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = v[j] * ks * w[j];
+      }
+      *reinterpret_cast<uint4*>(k_pool + ((pg * G + g) * m.page_tokens + ip) * dk + c) = hy_pack8(v);
+    }
+  }
+  if (off_v != off_k)
+    for (int i = threadIdx.x * 8; i < nv; i += 256 * 8) {
+      const int g = i / dv, c = i - g * dv;
+      float v[8];
+      hy_load8(prow + off_v + i, bias != nullptr ? bias + off_v + i : nullptr, v);
+      *reinterpret_cast<uint4*>(v_pool + ((pg * G + g) * m.page_tokens + ip) * dv + c) = hy_pack8(v);
+    }
+}
+
 // ----------------------------------------------------------------------------- rotary positions, value blending, head mixing
 // Rotation of the first `dims` entries of a head: entry pairs (i, i + dims/2) (half = 1) or (2i, 2i + 1) (half = 0);
 // (u, v) -> (u c - v s, v c + u s) with c, s = mult * cos / sin(pos * freq[i]).  The angle is formed in double and reduced

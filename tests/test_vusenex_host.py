@@ -54,6 +54,7 @@ def test_checkpoint_on_disk_round_trip(tmp_path):
   p = write_random_checkpoint(tmp_path / "m", raw, seed=1)
   cfg = load_model_config(p / "config.json")
   assert cfg["architecture"] == "Vusenex" and cfg["num_layers"] == len(raw["layers"])
+  assert cfg["pos_rows"] == raw["max_positions"]          # taken from the position table's rows
   sh = vusenex_param_shapes(raw)
   assert sh["l0.norm1"] == () and sh["final.norm"] == () and "l2.norm2" not in sh and "l2.rg2" not in sh and "l1.mlp.shared.up" not in sh
   assert sh["bigram"] == (raw["embedding"]["bigram"]["buckets"] + 1, raw["width"]) and sh["pos"] == (raw["max_positions"], raw["width"])

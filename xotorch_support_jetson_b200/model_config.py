@@ -288,6 +288,10 @@ def load_model_config(model_config_path: Path) -> dict:
     cfg = hybrid_model_config(hf)
     if any(lay.get("mixer") == "gdelta" and not lay.get("rank") for lay in cfg["layers"]):
       resolve_tensor_sizes(cfg, safetensors_shapes(Path(model_config_path).parent))
+    if cfg.get("pos_rows"):   # a learned position table: its own row count bounds the positions
+      rows = safetensors_shapes(Path(model_config_path).parent).get("pos")
+      if rows:
+        cfg["pos_rows"] = cfg["max_seq_len"] = int(rows[0])
     return cfg
   cfg = {ours: hf[theirs] for theirs, ours in _DIRECT_FIELDS}
   cfg.update({ours: hf.get(theirs, default) for theirs, ours, default in _OPTIONAL_FIELDS})
